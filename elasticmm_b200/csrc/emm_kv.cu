@@ -1,0 +1,901 @@
+// C ABI of the paged KV-cache movement library: contexts, pool descriptors,
+// argument validation and kernel launches. Declarations and the reference
+// methods each entry replaces are in include/emm_kv.h.
+#include "emm_kv.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "append.cuh"
+#include "page_copy.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define EMM_CUDA(call)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (call);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return fail(EMM_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_),  \
+                  __FILE__, __LINE__);                                                   \
+  } while (0)
+
+// Largest power of two (capped at 256) dividing v; 256 for v == 0.
+uint32_t pow2_align(uint64_t v) {
+  if (v == 0) return 256;
+  uint64_t a = v & (~v + 1);
+  return a > 256 ? 256u : (uint32_t)a;
+}
+
+constexpr int kRingSlots = 8;
+
+struct IdSlot {
+  int32_t *h = nullptr;  // pinned
+  int32_t *d = nullptr;
+  size_t cap = 0;        // ids
+  cudaEvent_t ev = nullptr;
+  bool pending = false;
+};
+
+struct IpcMapping {
+  unsigned char handle[EMM_IPC_HANDLE_BYTES];
+  void *base;
+};
+
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int dev) {
+    ok_ = cudaGetDevice(&prev_) == cudaSuccess;
+    if (ok_ && prev_ != dev) ok_ = cudaSetDevice(dev) == cudaSuccess;
+    changed_ = ok_ && prev_ != dev;
+  }
+  ~DeviceGuard() {
+    if (changed_) cudaSetDevice(prev_);
+  }
+  bool ok() const { return ok_; }
+
+ private:
+  int prev_ = 0;
+  bool ok_ = false;
+  bool changed_ = false;
+};
+
+}  // namespace
+
+struct emm_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int *d_status = nullptr;  // 4 ints: code, detail lo, detail hi, pad
+  int *h_status = nullptr;  // pinned mirror
+  int64_t launches = 0;
+  // options
+  int copy_variant = EMM_COPY_AUTO;
+  int64_t chunk_bytes = 0;  // 0 = per-variant default
+  int stages = 4;
+  int warps = 4;
+  int ctas_per_sm = 0;      // 0 = per-variant default
+  int ldg_unroll = 4;
+  int max_ctas = 0;
+  int bulk_smem_set = 0;    // dynamic smem limit already applied to the bulk kernel
+  IdSlot ring[kRingSlots];
+  int next_slot = 0;
+  std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
+  std::vector<IpcMapping> ipc;
+};
+
+struct emm_pool {
+  emm_ctx *ctx = nullptr;
+  emm_pool_desc desc{};
+  uint64_t *d_layers = nullptr;
+  std::vector<uint64_t> h_layers;
+  int64_t page_bytes = 0;
+  uint32_t align = 1;   // power-of-two alignment shared by all page addresses
+  bool device_local = true;  // every layer pointer is plain memory of ctx->device
+};
+
+namespace {
+
+using emm::CopySide;
+using emm::PageCopyArgs;
+
+// Checks the descriptor; on success *dense_page says whether a block of a
+// plane is one dense run of BS*H*D*e bytes.
+int check_desc(const emm_pool_desc &d, bool *dense_page) {
+  if (d.num_layers <= 0 || d.num_blocks <= 0 || d.block_size <= 0 || d.num_kv_heads <= 0 ||
+      d.head_size <= 0)
+    return fail(EMM_ERR_BAD_ARG, "pool geometry must be positive (L=%d NB=%d BS=%d H=%d D=%d)",
+                d.num_layers, d.num_blocks, d.block_size, d.num_kv_heads, d.head_size);
+  if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4 && d.elem_size != 8)
+    return fail(EMM_ERR_BAD_ARG, "elem_size %d not in {1,2,4,8}", d.elem_size);
+  const int64_t e = d.elem_size;
+  const int64_t head_bytes = (int64_t)d.head_size * e;
+  const int64_t page = (int64_t)d.block_size * d.num_kv_heads * head_bytes;
+  if (page > (int64_t)0x7fffffff) return fail(EMM_ERR_TOO_LARGE, "page of %lld bytes", (long long)page);
+  if (d.plane_stride < page || d.block_stride < page || d.token_stride < head_bytes ||
+      d.head_stride < head_bytes)
+    return fail(EMM_ERR_BAD_ARG, "strides smaller than the data they step over");
+  if (d.plane_stride % e || d.block_stride % e || d.token_stride % e || d.head_stride % e)
+    return fail(EMM_ERR_ALIGN, "strides must be multiples of elem_size");
+  const bool nhd = d.head_stride == head_bytes && d.token_stride == head_bytes * d.num_kv_heads;
+  const bool hnd = d.token_stride == head_bytes && d.head_stride == head_bytes * d.block_size;
+  *dense_page = nhd || hnd;
+  if (!*dense_page) {
+    // A strided page still supports append; whole-block moves are refused later.
+    const int64_t tok_span = (int64_t)(d.block_size - 1) * d.token_stride;
+    const int64_t head_span = (int64_t)(d.num_kv_heads - 1) * d.head_stride;
+    if (tok_span + head_span + head_bytes > d.block_stride)
+      return fail(EMM_ERR_BAD_ARG, "token/head strides run past block_stride");
+  }
+  return EMM_OK;
+}
+
+int acquire_slot(emm_ctx *ctx, size_t n_ids, IdSlot **out) {
+  IdSlot &s = ctx->ring[ctx->next_slot];
+  ctx->next_slot = (ctx->next_slot + 1) % kRingSlots;
+  if (s.pending) {
+    EMM_CUDA(cudaEventSynchronize(s.ev));  // normally long complete
+    s.pending = false;
+  }
+  if (!s.ev) EMM_CUDA(cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
+  if (s.cap < n_ids) {
+    size_t cap = std::max<size_t>(4096, s.cap * 2);
+    while (cap < n_ids) cap *= 2;
+    if (s.h) cudaFreeHost(s.h);
+    if (s.d) cudaFree(s.d);
+    s.h = nullptr;
+    s.d = nullptr;
+    s.cap = 0;
+    EMM_CUDA(cudaMallocHost(&s.h, cap * sizeof(int32_t)));
+    EMM_CUDA(cudaMalloc(&s.d, cap * sizeof(int32_t)));
+    s.cap = cap;
+  }
+  *out = &s;
+  return EMM_OK;
+}
+
+// Marks ids in the scratch bitmap. Returns false on the first id already set.
+bool bitmap_mark(std::vector<uint64_t> &bm, const int64_t *ids, int32_t n, int64_t *dup) {
+  for (int32_t i = 0; i < n; ++i) {
+    uint64_t w = (uint64_t)ids[i] >> 6, b = 1ull << (ids[i] & 63);
+    if (bm[w] & b) {
+      *dup = ids[i];
+      return false;
+    }
+    bm[w] |= b;
+  }
+  return true;
+}
+void bitmap_clear(std::vector<uint64_t> &bm, const int64_t *ids, int32_t n) {
+  for (int32_t i = 0; i < n; ++i) bm[(uint64_t)ids[i] >> 6] = 0;
+}
+
+int check_ids_host(const int64_t *ids, int32_t n, int64_t nb, const char *what) {
+  for (int32_t i = 0; i < n; ++i)
+    if (ids[i] < 0 || ids[i] >= nb)
+      return fail(EMM_ERR_ID_RANGE, "%s id %lld at position %d outside [0, %lld)", what,
+                  (long long)ids[i], i, (long long)nb);
+  return EMM_OK;
+}
+
+// One side of a copy backed by a pool.
+CopySide pool_side(const emm_pool *p, const int32_t *ids) {
+  CopySide s;
+  s.layers = p->d_layers;
+  s.base = 0;
+  s.layer_stride = 0;
+  s.plane_stride = (uint64_t)p->desc.plane_stride;
+  s.block_stride = (uint64_t)p->desc.block_stride;
+  s.ids = ids;
+  s.num_blocks = (uint32_t)p->desc.num_blocks;
+  return s;
+}
+
+// One side backed by the packed buffer [layers, 2, n, page].
+CopySide packed_side(const void *packed, int32_t n, int64_t page) {
+  CopySide s;
+  s.layers = nullptr;
+  s.base = (uint64_t)packed;
+  s.layer_stride = 2ull * (uint64_t)n * (uint64_t)page;
+  s.plane_stride = (uint64_t)n * (uint64_t)page;
+  s.block_stride = (uint64_t)page;
+  s.ids = nullptr;
+  s.num_blocks = (uint32_t)n;
+  return s;
+}
+
+template <typename V>
+int launch_ldg_typed(emm_ctx *ctx, const PageCopyArgs &a, int grid, cudaStream_t st) {
+  switch (ctx->ldg_unroll) {
+    case 1: emm::page_copy_ldg<V, 1><<<grid, 256, 0, st>>>(a); break;
+    case 2: emm::page_copy_ldg<V, 2><<<grid, 256, 0, st>>>(a); break;
+    case 8: emm::page_copy_ldg<V, 8><<<grid, 256, 0, st>>>(a); break;
+    default: emm::page_copy_ldg<V, 4><<<grid, 256, 0, st>>>(a); break;
+  }
+  return EMM_OK;
+}
+
+// Launches the page copy described by (src, dst). `align` is the common
+// power-of-two alignment of every address and length involved; `local` says
+// both sides are ordinary memory of this GPU.
+int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_t layer_begin,
+                     int32_t layer_count, int64_t page_bytes, uint32_t align, bool local,
+                     cudaStream_t st) {
+  if (n == 0 || layer_count == 0) return EMM_OK;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+
+  int variant = ctx->copy_variant;
+  if (variant == EMM_COPY_AUTO) variant = EMM_COPY_BULK;
+  if (align < 16 || !local) variant = EMM_COPY_LDG;
+
+  PageCopyArgs a;
+  a.src = src;
+  a.dst = dst;
+  a.n = (uint32_t)n;
+  a.layer_begin = (uint32_t)layer_begin;
+  a.layer_count = (uint32_t)layer_count;
+  a.page_bytes = (uint32_t)page_bytes;
+  a.status = ctx->d_status;
+
+  int64_t chunk = ctx->chunk_bytes;
+  if (chunk <= 0) chunk = (variant == EMM_COPY_BULK) ? 8192 : 256 * 16 * ctx->ldg_unroll;
+  if (chunk > page_bytes) chunk = page_bytes;
+  if (variant == EMM_COPY_BULK) {
+    // The ring of warps*stages chunks must fit the opt-in shared memory.
+    const int64_t budget = (int64_t)ctx->max_smem_optin - 2048;
+    while ((int64_t)ctx->warps * ctx->stages * chunk > budget && chunk > 1024) chunk /= 2;
+    chunk &= ~(int64_t)15;
+    if (chunk < 16 || (int64_t)ctx->warps * ctx->stages * chunk > budget)
+      return fail(EMM_ERR_BAD_ARG, "bulk ring of %d x %d chunks does not fit shared memory",
+                  ctx->warps, ctx->stages);
+  }
+  a.chunk_bytes = (uint32_t)chunk;
+  a.chunks_per_page = (uint32_t)((page_bytes + chunk - 1) / chunk);
+  a.total_chunks = (uint64_t)layer_count * 2ull * (uint64_t)n * a.chunks_per_page;
+
+  if (variant == EMM_COPY_BULK) {
+    const int smem = (int)((int64_t)ctx->warps * ctx->stages * chunk);
+    if (smem > ctx->bulk_smem_set) {
+      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      ctx->bulk_smem_set = smem;
+    }
+    int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm
+                                      : std::max(1, (int)((ctx->max_smem_optin - 2048) / (smem + 1024)));
+    per_sm = std::min(per_sm, 2048 / (ctx->warps * 32));
+    uint64_t want = (a.total_chunks + ctx->warps - 1) / ctx->warps;
+    uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
+    if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
+    const int grid = (int)std::min<uint64_t>(want, cap);
+    emm::page_copy_bulk<<<grid, ctx->warps * 32, smem, st>>>(a, (uint32_t)ctx->stages);
+  } else {
+    const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : 8;
+    uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
+    if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
+    const int grid = (int)std::min<uint64_t>(a.total_chunks, cap);
+    if (align >= 16) launch_ldg_typed<uint4>(ctx, a, grid, st);
+    else if (align >= 8) launch_ldg_typed<uint2>(ctx, a, grid, st);
+    else if (align >= 4) launch_ldg_typed<uint32_t>(ctx, a, grid, st);
+    else if (align >= 2) launch_ldg_typed<uint16_t>(ctx, a, grid, st);
+    else launch_ldg_typed<uint8_t>(ctx, a, grid, st);
+  }
+  EMM_CUDA(cudaGetLastError());
+  ctx->launches += 1;
+  return EMM_OK;
+}
+
+int check_pool_for_pages(const emm_pool *p, const char *what) {
+  if (!p) return fail(EMM_ERR_BAD_ARG, "%s: null pool", what);
+  if (p->page_bytes == 0)
+    return fail(EMM_ERR_BAD_ARG, "%s: pool pages are not dense; whole-block moves unsupported", what);
+  return EMM_OK;
+}
+
+int check_layer_range(const emm_pool *p, int32_t begin, int32_t count) {
+  if (begin < 0 || count < 0 || (int64_t)begin + count > p->desc.num_layers)
+    return fail(EMM_ERR_BAD_ARG, "layer range [%d, %d) outside [0, %d)", begin, begin + count,
+                p->desc.num_layers);
+  return EMM_OK;
+}
+
+int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t layer_count,
+                const int32_t *d_ids, int32_t n, const void *d_packed, uint64_t packed_bytes,
+                void *stream) {
+  const char *what = to_packed ? "gather" : "scatter";
+  if (int rc = check_pool_for_pages(pool, what)) return rc;
+  if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "%s: negative block count %d", what, n);
+  const uint64_t want = (uint64_t)layer_count * 2ull * (uint64_t)n * (uint64_t)pool->page_bytes;
+  if (packed_bytes != want)
+    return fail(EMM_ERR_LENGTH, "%s: packed buffer holds %llu bytes, %d blocks need %llu", what,
+                (unsigned long long)packed_bytes, n, (unsigned long long)want);
+  if (n == 0 || layer_count == 0) return EMM_OK;
+  if (!d_ids || !d_packed) return fail(EMM_ERR_BAD_ARG, "%s: null pointer", what);
+  const uint32_t align = std::min(pool->align, pow2_align((uint64_t)d_packed));
+  if (align < (uint32_t)pool->desc.elem_size)
+    return fail(EMM_ERR_ALIGN, "%s: packed buffer not aligned to elem_size", what);
+  CopySide ps = pool_side(pool, d_ids);
+  CopySide bs = packed_side(d_packed, n, pool->page_bytes);
+  return to_packed ? launch_page_copy(pool->ctx, ps, bs, n, layer_begin, layer_count,
+                                      pool->page_bytes, align, pool->device_local,
+                                      (cudaStream_t)stream)
+                   : launch_page_copy(pool->ctx, bs, ps, n, layer_begin, layer_count,
+                                      pool->page_bytes, align, pool->device_local,
+                                      (cudaStream_t)stream);
+}
+
+// Uploads host ids (already validated) into a ring slot; returns the device
+// pointers of the first and (optional) second table.
+int upload_ids(emm_ctx *ctx, const int64_t *a, const int64_t *b, int32_t n, cudaStream_t st,
+               IdSlot **slot_out, const int32_t **d_a, const int32_t **d_b) {
+  IdSlot *s = nullptr;
+  const size_t total = (size_t)n * (b ? 2 : 1);
+  if (int rc = acquire_slot(ctx, total, &s)) return rc;
+  for (int32_t i = 0; i < n; ++i) s->h[i] = (int32_t)a[i];
+  if (b)
+    for (int32_t i = 0; i < n; ++i) s->h[n + i] = (int32_t)b[i];
+  EMM_CUDA(cudaMemcpyAsync(s->d, s->h, total * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  *d_a = s->d;
+  if (d_b) *d_b = b ? s->d + n : nullptr;
+  *slot_out = s;
+  return EMM_OK;
+}
+
+int finish_slot(IdSlot *s, cudaStream_t st) {
+  EMM_CUDA(cudaEventRecord(s->ev, st));
+  s->pending = true;
+  return EMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int emm_abi_version(void) { return EMM_KV_ABI_VERSION; }
+
+const char *emm_status_string(int status) {
+  switch (status) {
+    case EMM_OK: return "ok";
+    case EMM_ERR_BAD_ARG: return "bad argument";
+    case EMM_ERR_ID_RANGE: return "block id or slot out of range";
+    case EMM_ERR_LENGTH: return "length mismatch";
+    case EMM_ERR_CUDA: return "CUDA error";
+    case EMM_ERR_TIMEOUT: return "device-side wait timed out";
+    case EMM_ERR_ALIGN: return "misaligned pointer or stride";
+    case EMM_ERR_DUPLICATE: return "duplicate destination id";
+    case EMM_ERR_OVERLAP: return "source and destination ids overlap";
+    case EMM_ERR_TOO_LARGE: return "size exceeds capacity";
+    case EMM_ERR_NOMEM: return "out of memory";
+    default: return "unknown status";
+  }
+}
+
+const char *emm_last_error(void) { return g_last_error.c_str(); }
+
+int emm_ctx_create(int device, emm_ctx **out) {
+  if (!out) return fail(EMM_ERR_BAD_ARG, "emm_ctx_create: null out");
+  *out = nullptr;
+  int count = 0;
+  EMM_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count)
+    return fail(EMM_ERR_BAD_ARG, "device %d not in [0, %d)", device, count);
+  DeviceGuard guard(device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", device);
+  emm_ctx *ctx = new (std::nothrow) emm_ctx();
+  if (!ctx) return fail(EMM_ERR_NOMEM, "emm_ctx_create: host allocation failed");
+  ctx->device = device;
+  cudaError_t e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (e == cudaSuccess)
+    e = cudaDeviceGetAttribute(&ctx->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&ctx->h_status, 4 * sizeof(int));
+  if (e != cudaSuccess) {
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    delete ctx;
+    return fail(EMM_ERR_CUDA, "emm_ctx_create: %s", cudaGetErrorString(e));
+  }
+  *out = ctx;
+  return EMM_OK;
+}
+
+int emm_ctx_destroy(emm_ctx *ctx) {
+  if (!ctx) return EMM_OK;
+  DeviceGuard guard(ctx->device);
+  cudaDeviceSynchronize();
+  for (IdSlot &s : ctx->ring) {
+    if (s.h) cudaFreeHost(s.h);
+    if (s.d) cudaFree(s.d);
+    if (s.ev) cudaEventDestroy(s.ev);
+  }
+  for (IpcMapping &m : ctx->ipc) cudaIpcCloseMemHandle(m.base);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  delete ctx;
+  return EMM_OK;
+}
+
+int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
+  if (!ctx) return fail(EMM_ERR_BAD_ARG, "null context");
+  switch (option) {
+    case EMM_OPT_COPY_VARIANT:
+      if (value < EMM_COPY_AUTO || value > EMM_COPY_LDG)
+        return fail(EMM_ERR_BAD_ARG, "copy variant %lld unknown", (long long)value);
+      ctx->copy_variant = (int)value;
+      return EMM_OK;
+    case EMM_OPT_CHUNK_BYTES:
+      if (value < 0 || value % 16 || value > (1 << 20))
+        return fail(EMM_ERR_BAD_ARG, "chunk bytes must be a multiple of 16 in [0, 1 MiB]");
+      ctx->chunk_bytes = value;
+      return EMM_OK;
+    case EMM_OPT_STAGES:
+      if (value < 2 || value > emm::kMaxStages)
+        return fail(EMM_ERR_BAD_ARG, "stages must be in [2, %d]", emm::kMaxStages);
+      ctx->stages = (int)value;
+      return EMM_OK;
+    case EMM_OPT_WARPS:
+      if (value < 1 || value > emm::kMaxWarps)
+        return fail(EMM_ERR_BAD_ARG, "warps must be in [1, %d]", emm::kMaxWarps);
+      ctx->warps = (int)value;
+      return EMM_OK;
+    case EMM_OPT_CTAS_PER_SM:
+      if (value < 0 || value > 32) return fail(EMM_ERR_BAD_ARG, "CTAs per SM must be in [0, 32]");
+      ctx->ctas_per_sm = (int)value;
+      return EMM_OK;
+    case EMM_OPT_LDG_UNROLL:
+      if (value != 1 && value != 2 && value != 4 && value != 8)
+        return fail(EMM_ERR_BAD_ARG, "LDG unroll must be 1, 2, 4 or 8");
+      ctx->ldg_unroll = (int)value;
+      return EMM_OK;
+    case EMM_OPT_MAX_CTAS:
+      if (value < 0 || value > (1 << 20)) return fail(EMM_ERR_BAD_ARG, "max CTAs out of range");
+      ctx->max_ctas = (int)value;
+      return EMM_OK;
+    default:
+      return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
+  }
+}
+
+int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
+  if (!ctx || !value) return fail(EMM_ERR_BAD_ARG, "null argument");
+  switch (option) {
+    case EMM_OPT_COPY_VARIANT: *value = ctx->copy_variant; return EMM_OK;
+    case EMM_OPT_CHUNK_BYTES: *value = ctx->chunk_bytes; return EMM_OK;
+    case EMM_OPT_STAGES: *value = ctx->stages; return EMM_OK;
+    case EMM_OPT_WARPS: *value = ctx->warps; return EMM_OK;
+    case EMM_OPT_CTAS_PER_SM: *value = ctx->ctas_per_sm; return EMM_OK;
+    case EMM_OPT_LDG_UNROLL: *value = ctx->ldg_unroll; return EMM_OK;
+    case EMM_OPT_MAX_CTAS: *value = ctx->max_ctas; return EMM_OK;
+    default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
+  }
+}
+
+int64_t emm_ctx_launch_count(emm_ctx *ctx) { return ctx ? ctx->launches : -1; }
+
+int emm_ctx_status(emm_ctx *ctx, void *stream, int64_t *detail) {
+  if (!ctx) return fail(EMM_ERR_BAD_ARG, "null context");
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  EMM_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, 4 * sizeof(int), cudaMemcpyDeviceToHost, st));
+  EMM_CUDA(cudaMemsetAsync(ctx->d_status, 0, 4 * sizeof(int), st));
+  EMM_CUDA(cudaStreamSynchronize(st));
+  const int code = ctx->h_status[0];
+  const int64_t d = (int64_t)(((uint64_t)(uint32_t)ctx->h_status[2] << 32) | (uint32_t)ctx->h_status[1]);
+  if (detail) *detail = d;
+  if (code != EMM_OK)
+    return fail(code, "device reported '%s' (detail %lld)", emm_status_string(code), (long long)d);
+  return EMM_OK;
+}
+
+static int fill_desc(emm_pool_desc *d, int L, int NB, int BS, int H, int D, int e, bool hnd) {
+  if (!d) return fail(EMM_ERR_BAD_ARG, "null descriptor");
+  d->num_layers = L;
+  d->num_blocks = NB;
+  d->block_size = BS;
+  d->num_kv_heads = H;
+  d->head_size = D;
+  d->elem_size = e;
+  const int64_t head_bytes = (int64_t)D * e;
+  const int64_t page = (int64_t)BS * H * head_bytes;
+  d->block_stride = page;
+  d->plane_stride = page * NB;
+  if (hnd) {
+    d->token_stride = head_bytes;
+    d->head_stride = head_bytes * BS;
+  } else {
+    d->token_stride = head_bytes * H;
+    d->head_stride = head_bytes;
+  }
+  bool dense;
+  return check_desc(*d, &dense);
+}
+
+int emm_pool_desc_nhd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, int elem_size) {
+  return fill_desc(desc, L, NB, BS, H, D, elem_size, false);
+}
+
+int emm_pool_desc_hnd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, int elem_size) {
+  return fill_desc(desc, L, NB, BS, H, D, elem_size, true);
+}
+
+int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *layer_ptrs,
+                    emm_pool **out) {
+  if (!ctx || !desc || !layer_ptrs || !out) return fail(EMM_ERR_BAD_ARG, "emm_pool_create: null argument");
+  *out = nullptr;
+  bool dense = false;
+  if (int rc = check_desc(*desc, &dense)) return rc;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+
+  emm_pool *p = new (std::nothrow) emm_pool();
+  if (!p) return fail(EMM_ERR_NOMEM, "emm_pool_create: host allocation failed");
+  p->ctx = ctx;
+  p->desc = *desc;
+  p->page_bytes = dense ? (int64_t)desc->block_size * desc->num_kv_heads * desc->head_size * desc->elem_size : 0;
+  uint32_t align = std::min(pow2_align((uint64_t)desc->plane_stride), pow2_align((uint64_t)desc->block_stride));
+  if (dense) align = std::min(align, pow2_align((uint64_t)p->page_bytes));
+  p->h_layers.resize(desc->num_layers);
+  for (int l = 0; l < desc->num_layers; ++l) {
+    if (!layer_ptrs[l]) {
+      delete p;
+      return fail(EMM_ERR_BAD_ARG, "layer %d base pointer is null", l);
+    }
+    p->h_layers[l] = (uint64_t)layer_ptrs[l];
+    align = std::min(align, pow2_align(p->h_layers[l]));
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, layer_ptrs[l]);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      p->device_local = false;
+    } else if (attr.type != cudaMemoryTypeDevice || attr.device != ctx->device) {
+      p->device_local = false;
+    }
+  }
+  if (align < (uint32_t)desc->elem_size) {
+    delete p;
+    return fail(EMM_ERR_ALIGN, "layer base pointers not aligned to elem_size");
+  }
+  p->align = align;
+  cudaError_t e = cudaMalloc(&p->d_layers, sizeof(uint64_t) * desc->num_layers);
+  if (e == cudaSuccess)
+    e = cudaMemcpy(p->d_layers, p->h_layers.data(), sizeof(uint64_t) * desc->num_layers,
+                   cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (p->d_layers) cudaFree(p->d_layers);
+    delete p;
+    return fail(EMM_ERR_CUDA, "emm_pool_create: %s", cudaGetErrorString(e));
+  }
+  *out = p;
+  return EMM_OK;
+}
+
+int emm_pool_destroy(emm_pool *pool) {
+  if (!pool) return EMM_OK;
+  DeviceGuard guard(pool->ctx->device);
+  if (pool->d_layers) cudaFree(pool->d_layers);
+  delete pool;
+  return EMM_OK;
+}
+
+int emm_pool_get_desc(const emm_pool *pool, emm_pool_desc *desc) {
+  if (!pool || !desc) return fail(EMM_ERR_BAD_ARG, "null argument");
+  *desc = pool->desc;
+  return EMM_OK;
+}
+
+int64_t emm_pool_page_bytes(const emm_pool *pool) { return pool ? pool->page_bytes : -1; }
+
+int emm_gather(emm_pool *pool, const int32_t *d_ids, int32_t n, void *d_packed,
+               uint64_t packed_bytes, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "gather: null pool");
+  return packed_copy(pool, true, 0, pool->desc.num_layers, d_ids, n, d_packed, packed_bytes, stream);
+}
+
+int emm_scatter(emm_pool *pool, const int32_t *d_ids, int32_t n, const void *d_packed,
+                uint64_t packed_bytes, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "scatter: null pool");
+  return packed_copy(pool, false, 0, pool->desc.num_layers, d_ids, n, d_packed, packed_bytes, stream);
+}
+
+int emm_gather_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
+                      const int32_t *d_ids, int32_t n, void *d_packed, uint64_t packed_bytes,
+                      void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "gather: null pool");
+  return packed_copy(pool, true, layer_begin, layer_count, d_ids, n, d_packed, packed_bytes, stream);
+}
+
+int emm_scatter_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
+                       const int32_t *d_ids, int32_t n, const void *d_packed,
+                       uint64_t packed_bytes, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "scatter: null pool");
+  return packed_copy(pool, false, layer_begin, layer_count, d_ids, n, d_packed, packed_bytes, stream);
+}
+
+int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
+                    const int32_t *d_dst_ids, int32_t n, void *stream) {
+  if (int rc = check_pool_for_pages(src, "copy_blocks(src)")) return rc;
+  if (int rc = check_pool_for_pages(dst, "copy_blocks(dst)")) return rc;
+  if (src->ctx != dst->ctx) return fail(EMM_ERR_BAD_ARG, "copy_blocks: pools of different contexts");
+  if (src->page_bytes != dst->page_bytes || src->desc.num_layers != dst->desc.num_layers)
+    return fail(EMM_ERR_LENGTH, "copy_blocks: pools differ in page size (%lld vs %lld) or layers (%d vs %d)",
+                (long long)src->page_bytes, (long long)dst->page_bytes, src->desc.num_layers,
+                dst->desc.num_layers);
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "copy_blocks: negative block count");
+  if (n == 0) return EMM_OK;
+  if (!d_src_ids || !d_dst_ids) return fail(EMM_ERR_BAD_ARG, "copy_blocks: null id table");
+  return launch_page_copy(src->ctx, pool_side(src, d_src_ids), pool_side(dst, d_dst_ids), n, 0,
+                          src->desc.num_layers, src->page_bytes, std::min(src->align, dst->align),
+                          src->device_local && dst->device_local, (cudaStream_t)stream);
+}
+
+int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed,
+                 uint64_t packed_bytes, void *stream) {
+  if (int rc = check_pool_for_pages(pool, "gather")) return rc;
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "gather: negative block count");
+  if (n > 0 && !h_ids) return fail(EMM_ERR_BAD_ARG, "gather: null id list");
+  if (int rc = check_ids_host(h_ids, n, pool->desc.num_blocks, "gather")) return rc;
+  if (n == 0) return packed_copy(pool, true, 0, pool->desc.num_layers, nullptr, 0, d_packed, packed_bytes, stream);
+  DeviceGuard guard(pool->ctx->device);
+  IdSlot *slot;
+  const int32_t *d_ids;
+  if (int rc = upload_ids(pool->ctx, h_ids, nullptr, n, (cudaStream_t)stream, &slot, &d_ids, nullptr)) return rc;
+  int rc = packed_copy(pool, true, 0, pool->desc.num_layers, d_ids, n, d_packed, packed_bytes, stream);
+  int rc2 = finish_slot(slot, (cudaStream_t)stream);
+  return rc ? rc : rc2;
+}
+
+int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d_packed,
+                  uint64_t packed_bytes, void *stream) {
+  if (int rc = check_pool_for_pages(pool, "scatter")) return rc;
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "scatter: negative block count");
+  if (n > 0 && !h_ids) return fail(EMM_ERR_BAD_ARG, "scatter: null id list");
+  if (int rc = check_ids_host(h_ids, n, pool->desc.num_blocks, "scatter")) return rc;
+  if (n == 0) return packed_copy(pool, false, 0, pool->desc.num_layers, nullptr, 0, d_packed, packed_bytes, stream);
+  emm_ctx *ctx = pool->ctx;
+  const size_t words = ((size_t)pool->desc.num_blocks + 63) / 64;
+  if (ctx->bitmap.size() < words) ctx->bitmap.resize(words);
+  int64_t dup = -1;
+  const bool unique = bitmap_mark(ctx->bitmap, h_ids, n, &dup);
+  bitmap_clear(ctx->bitmap, h_ids, n);
+  if (!unique) return fail(EMM_ERR_DUPLICATE, "scatter: destination id %lld appears twice", (long long)dup);
+  DeviceGuard guard(ctx->device);
+  IdSlot *slot;
+  const int32_t *d_ids;
+  if (int rc = upload_ids(ctx, h_ids, nullptr, n, (cudaStream_t)stream, &slot, &d_ids, nullptr)) return rc;
+  int rc = packed_copy(pool, false, 0, pool->desc.num_layers, d_ids, n, d_packed, packed_bytes, stream);
+  int rc2 = finish_slot(slot, (cudaStream_t)stream);
+  return rc ? rc : rc2;
+}
+
+int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
+                      const int64_t *h_dst_ids, int32_t n, void *stream) {
+  if (int rc = check_pool_for_pages(src, "copy_blocks(src)")) return rc;
+  if (int rc = check_pool_for_pages(dst, "copy_blocks(dst)")) return rc;
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "copy_blocks: negative block count");
+  if (n == 0) return EMM_OK;
+  if (!h_src_ids || !h_dst_ids) return fail(EMM_ERR_BAD_ARG, "copy_blocks: null id list");
+  if (int rc = check_ids_host(h_src_ids, n, src->desc.num_blocks, "copy_blocks source")) return rc;
+  if (int rc = check_ids_host(h_dst_ids, n, dst->desc.num_blocks, "copy_blocks destination")) return rc;
+  emm_ctx *ctx = src->ctx;
+  const size_t words = ((size_t)std::max(src->desc.num_blocks, dst->desc.num_blocks) + 63) / 64;
+  if (ctx->bitmap.size() < words) ctx->bitmap.resize(words);
+  int64_t dup = -1;
+  bool ok = bitmap_mark(ctx->bitmap, h_dst_ids, n, &dup);
+  int rc_check = EMM_OK;
+  if (!ok) {
+    rc_check = fail(EMM_ERR_DUPLICATE, "copy_blocks: destination id %lld appears twice", (long long)dup);
+  } else if (src == dst || (src->h_layers == dst->h_layers)) {
+    // Same memory: a source that is also a destination would be read and
+    // written by different CTAs in an undefined order.
+    for (int32_t i = 0; i < n; ++i) {
+      const uint64_t w = (uint64_t)h_src_ids[i] >> 6, b = 1ull << (h_src_ids[i] & 63);
+      if (ctx->bitmap[w] & b) {
+        rc_check = fail(EMM_ERR_OVERLAP, "copy_blocks: block %lld is both source and destination",
+                        (long long)h_src_ids[i]);
+        break;
+      }
+    }
+  }
+  bitmap_clear(ctx->bitmap, h_dst_ids, n);
+  if (rc_check) return rc_check;
+  DeviceGuard guard(ctx->device);
+  IdSlot *slot;
+  const int32_t *d_s, *d_d;
+  if (int rc = upload_ids(ctx, h_src_ids, h_dst_ids, n, (cudaStream_t)stream, &slot, &d_s, &d_d)) return rc;
+  int rc = emm_copy_blocks(src, dst, d_s, d_d, n, stream);
+  int rc2 = finish_slot(slot, (cudaStream_t)stream);
+  return rc ? rc : rc2;
+}
+
+static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const void *d_key,
+                       const void *d_value, int64_t kls, int64_t kts, int64_t vls, int64_t vts,
+                       const int64_t *d_slots, int32_t T, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "append: null pool");
+  if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
+  if (T < 0) return fail(EMM_ERR_BAD_ARG, "append: negative token count");
+  if (T == 0 || layer_count == 0) return EMM_OK;
+  if (!d_key || !d_value || !d_slots) return fail(EMM_ERR_BAD_ARG, "append: null pointer");
+  const emm_pool_desc &d = pool->desc;
+  const int64_t head_bytes = (int64_t)d.head_size * d.elem_size;
+  const int64_t row_bytes = head_bytes * d.num_kv_heads;
+  if (kts < row_bytes || vts < row_bytes)
+    return fail(EMM_ERR_BAD_ARG, "append: token stride smaller than a token row (%lld bytes)", (long long)row_bytes);
+  if (layer_count > 1 && (kls < (int64_t)T * row_bytes || vls < (int64_t)T * row_bytes))
+    return fail(EMM_ERR_BAD_ARG, "append: layer stride smaller than one layer of rows");
+  emm_ctx *ctx = pool->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+
+  uint32_t align = pow2_align((uint64_t)head_bytes);
+  for (int l = 0; l < d.num_layers; ++l) align = std::min(align, pow2_align(pool->h_layers[l]));
+  const uint64_t parts[] = {(uint64_t)d.plane_stride, (uint64_t)d.block_stride, (uint64_t)d.token_stride,
+                            (uint64_t)d.head_stride,  (uint64_t)d_key,          (uint64_t)d_value,
+                            (uint64_t)kts,            (uint64_t)vts,
+                            layer_count > 1 ? (uint64_t)kls : 0, layer_count > 1 ? (uint64_t)vls : 0};
+  for (uint64_t v : parts) align = std::min(align, pow2_align(v));
+  if (align < (uint32_t)d.elem_size) return fail(EMM_ERR_ALIGN, "append: key/value not aligned to elem_size");
+
+  emm::AppendArgs a;
+  a.layers = pool->d_layers;
+  a.plane_stride = (uint64_t)d.plane_stride;
+  a.block_stride = (uint64_t)d.block_stride;
+  a.token_stride = (uint64_t)d.token_stride;
+  a.head_stride = (uint64_t)d.head_stride;
+  a.num_slots = (uint64_t)d.num_blocks * (uint64_t)d.block_size;
+  a.block_size = (uint32_t)d.block_size;
+  a.head_bytes = (uint32_t)head_bytes;
+  a.row_bytes = (uint32_t)row_bytes;
+  a.layer_begin = (uint32_t)layer_begin;
+  a.layer_count = (uint32_t)layer_count;
+  a.num_tokens = (uint32_t)T;
+  a.key = (uint64_t)d_key;
+  a.value = (uint64_t)d_value;
+  a.key_layer_stride = (uint64_t)kls;
+  a.key_token_stride = (uint64_t)kts;
+  a.value_layer_stride = (uint64_t)vls;
+  a.value_token_stride = (uint64_t)vts;
+  a.slots = d_slots;
+  a.status = ctx->d_status;
+
+  const uint64_t rows = (uint64_t)layer_count * (uint64_t)T * 2ull;
+  const uint64_t grid64 = (rows + emm::kAppendWarps - 1) / emm::kAppendWarps;
+  if (grid64 > 0x7fffffffull) return fail(EMM_ERR_TOO_LARGE, "append: %llu rows", (unsigned long long)rows);
+  const int grid = (int)grid64;
+  const int block = emm::kAppendWarps * 32;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 2) emm::append_rows<uint16_t, 4><<<grid, block, 0, st>>>(a);
+  else emm::append_rows<uint8_t, 4><<<grid, block, 0, st>>>(a);
+  EMM_CUDA(cudaGetLastError());
+  ctx->launches += 1;
+  return EMM_OK;
+}
+
+int emm_append(emm_pool *pool, int32_t layer, const void *d_key, const void *d_value,
+               int64_t key_token_stride, int64_t value_token_stride,
+               const int64_t *d_slot_mapping, int32_t num_tokens, void *stream) {
+  return append_impl(pool, layer, 1, d_key, d_value, 0, key_token_stride, 0, value_token_stride,
+                     d_slot_mapping, num_tokens, stream);
+}
+
+int emm_append_all_layers(emm_pool *pool, const void *d_key, const void *d_value,
+                          int64_t key_layer_stride, int64_t key_token_stride,
+                          int64_t value_layer_stride, int64_t value_token_stride,
+                          const int64_t *d_slot_mapping, int32_t num_tokens, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "append: null pool");
+  return append_impl(pool, 0, pool->desc.num_layers, d_key, d_value, key_layer_stride,
+                     key_token_stride, value_layer_stride, value_token_stride, d_slot_mapping,
+                     num_tokens, stream);
+}
+
+int emm_compact_plan(const int64_t *table_ids, int64_t n_ids, int64_t num_blocks,
+                     int64_t *new_table_ids, int64_t *move_src, int64_t *move_dst,
+                     int64_t *n_moves) {
+  if (n_ids < 0 || num_blocks <= 0 || !n_moves) return fail(EMM_ERR_BAD_ARG, "compact_plan: bad argument");
+  *n_moves = 0;
+  if (n_ids == 0) return EMM_OK;
+  if (!table_ids || !new_table_ids || !move_src || !move_dst)
+    return fail(EMM_ERR_BAD_ARG, "compact_plan: null pointer");
+  if (n_ids > num_blocks)
+    return fail(EMM_ERR_LENGTH, "compact_plan: %lld live ids in a pool of %lld blocks", (long long)n_ids,
+                (long long)num_blocks);
+  // occupied[b] for b < n_ids: a live block already sits in the dense prefix.
+  std::vector<uint8_t> seen((size_t)num_blocks, 0);
+  for (int64_t i = 0; i < n_ids; ++i) {
+    const int64_t id = table_ids[i];
+    if (id < 0 || id >= num_blocks)
+      return fail(EMM_ERR_ID_RANGE, "compact_plan: id %lld at position %lld outside [0, %lld)", (long long)id,
+                  (long long)i, (long long)num_blocks);
+    if (seen[(size_t)id])
+      return fail(EMM_ERR_DUPLICATE, "compact_plan: block %lld belongs to two table entries", (long long)id);
+    seen[(size_t)id] = 1;
+  }
+  int64_t hole = 0;  // next candidate free id inside the prefix
+  int64_t moves = 0;
+  for (int64_t i = 0; i < n_ids; ++i) {
+    const int64_t id = table_ids[i];
+    if (id < n_ids) {
+      new_table_ids[i] = id;
+      continue;
+    }
+    while (seen[(size_t)hole]) ++hole;  // a hole exists: #live outside prefix == #holes inside
+    move_src[moves] = id;
+    move_dst[moves] = hole;
+    new_table_ids[i] = hole;
+    ++hole;
+    ++moves;
+  }
+  *n_moves = moves;
+  return EMM_OK;
+}
+
+int emm_ipc_export(emm_ctx *ctx, const void *d_ptr, unsigned char handle[EMM_IPC_HANDLE_BYTES],
+                   uint64_t *offset) {
+  if (!ctx || !d_ptr || !handle || !offset) return fail(EMM_ERR_BAD_ARG, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == EMM_IPC_HANDLE_BYTES, "IPC handle size");
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  // The handle names the whole allocation; find its base through the driver.
+  typedef int (*GetRangeFn)(unsigned long long *, size_t *, unsigned long long);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  EMM_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess)
+    return fail(EMM_ERR_CUDA, "ipc_export: driver entry point cuMemGetAddressRange unavailable");
+  unsigned long long base = 0;
+  size_t size = 0;
+  const int drc = ((GetRangeFn)fn)(&base, &size, (unsigned long long)d_ptr);
+  if (drc != 0) return fail(EMM_ERR_CUDA, "ipc_export: cuMemGetAddressRange returned %d", drc);
+  cudaIpcMemHandle_t h;
+  EMM_CUDA(cudaIpcGetMemHandle(&h, (void *)base));
+  memcpy(handle, &h, EMM_IPC_HANDLE_BYTES);
+  *offset = (uint64_t)d_ptr - (uint64_t)base;
+  return EMM_OK;
+}
+
+int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES], uint64_t offset,
+                 void **d_ptr) {
+  if (!ctx || !handle || !d_ptr) return fail(EMM_ERR_BAD_ARG, "ipc_open: null argument");
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  for (const IpcMapping &m : ctx->ipc) {
+    if (memcmp(m.handle, handle, EMM_IPC_HANDLE_BYTES) == 0) {
+      *d_ptr = (char *)m.base + offset;
+      return EMM_OK;
+    }
+  }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, EMM_IPC_HANDLE_BYTES);
+  void *base = nullptr;
+  EMM_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  IpcMapping m;
+  memcpy(m.handle, handle, EMM_IPC_HANDLE_BYTES);
+  m.base = base;
+  ctx->ipc.push_back(m);
+  *d_ptr = (char *)base + offset;
+  return EMM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,205 @@
+"""KV transfer orchestration with the reference's manager surface.
+
+Mirrors V0KVTransferManager (elasticmm/engine/v0/kv_transfer.py): a registry
+of workers keyed by global rank that survives role switches (:114-174),
+`transfer_kv_cache(request_id, src_rank, dst_rank, src_blocks, dst_blocks)
+-> bool` (:224-262), byte/time counters that leave out the first (cold)
+transfer (:506-515, :843-859) and a metrics callback called as
+`metrics_callback(transfer_time_sec=..., num_blocks=...)` for every transfer
+(:518-519).
+
+The reference's manager lives in a driver process and reaches workers through
+Ray actor handles. Here a manager lives in each worker process (one process
+per GPU): it holds the local worker object(s) and knows the other ranks only
+by number. A transfer whose source and sink are both local runs entirely in
+this process; otherwise this process performs its half (send or push on the
+source, receive on the sink) and the peer process performs the other half by
+making the same call.
+
+Added: TransferMethod.B200_PEER (direct stores into the sink's mapped pool)
+and `transfer_many(plan)`, which moves all requests of a role switch as one
+table per (source, sink) pair instead of one call per request
+(the reference serialises them, elasticmm/engine/v0/backend.py:674-718).
+"""
+from __future__ import annotations
+
+import time
+from enum import Enum
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .transport import MigrationPlan, Transfer
+
+
+class TransferMethod(Enum):
+    CUDA_IPC = "cuda_ipc"      # accepted as an alias of B200_PEER
+    NCCL = "nccl"              # staged: pack -> NCCL send/recv -> unpack, pipelined by layer chunk
+    P2P_COPY = "p2p_copy"      # extract on the source, write on the sink (both workers in this process)
+    STAGED_COPY = "staged_copy"  # not implemented in the reference either (a sleep); refused here
+    B200_PEER = "b200_peer"    # one kernel: local loads, stores into the sink's peer-mapped pool
+
+
+class V0KVTransferManager:
+    def __init__(self, transfer_method: TransferMethod = TransferMethod.P2P_COPY, nccl_coordinator=None,
+                 enable_batching: bool = False, batch_size: int = 3, batch_timeout: float = 0.005,
+                 metrics_callback: Optional[Callable[..., None]] = None):
+        self.transfer_method = transfer_method
+        self.nccl_coordinator = nccl_coordinator
+        self.enable_batching = enable_batching  # kept for signature parity; see transfer_many
+        self.metrics_callback = metrics_callback
+        self.worker_registry: Dict[int, Any] = {}
+        self.rank_to_stage: Dict[int, str] = {}
+        self.ipc_mem_handles: Dict[str, Dict[int, Dict[str, Any]]] = {}
+        self.transfer_count = 0
+        self.total_transfer_time = 0.0
+        self.total_bytes_transferred = 0
+        self.first_transfer_done = False
+
+    # -- registry --------------------------------------------------------------
+    @staticmethod
+    def _normalize_stage(stage: Any) -> str:
+        return str(getattr(stage, "value", stage)).lower()
+
+    def register_worker(self, global_rank: int, worker: Any, stage: str) -> None:
+        self.worker_registry[global_rank] = worker
+        self.rank_to_stage[global_rank] = self._normalize_stage(stage)
+
+    def register_workers(self, stage: str, workers: Sequence[Any], global_ranks: Sequence[int]) -> None:
+        for worker, rank in zip(workers, global_ranks):
+            if worker is not None and rank >= 0:
+                self.register_worker(rank, worker, stage)
+
+    def unregister_worker(self, global_rank: int) -> None:
+        self.worker_registry.pop(global_rank, None)
+        self.rank_to_stage.pop(global_rank, None)
+
+    def update_worker_stage(self, global_rank: int, new_stage: str) -> None:
+        """Role switch: only the stage label changes, the rank key stays."""
+        if global_rank in self.worker_registry:
+            self.rank_to_stage[global_rank] = self._normalize_stage(new_stage)
+
+    def register_ipc_handle(self, stage: str, worker_id: int, cache_type: str, ipc_handle: Any) -> None:
+        self.ipc_mem_handles.setdefault(stage, {}).setdefault(worker_id, {})[cache_type] = ipc_handle
+
+    # -- transfers ---------------------------------------------------------------
+    def _account(self, elapsed: float, nbytes: int, nblocks: int, count: int = 1) -> None:
+        if self.transfer_method == TransferMethod.P2P_COPY:
+            # the reference's copy path only counts transfers (kv_transfer.py:740)
+            self.transfer_count += count
+        elif not self.first_transfer_done:
+            self.first_transfer_done = True  # cold start: not part of the averages (:506-515)
+        else:
+            self.transfer_count += count
+            self.total_transfer_time += elapsed
+            self.total_bytes_transferred += nbytes
+        if self.metrics_callback:
+            self.metrics_callback(transfer_time_sec=elapsed, num_blocks=nblocks)
+
+    def _run(self, src_rank: int, dst_rank: int, src_blocks: List[int], dst_blocks: List[int]) -> Dict[str, Any]:
+        src = self.worker_registry.get(src_rank)
+        dst = self.worker_registry.get(dst_rank)
+        method = self.transfer_method
+        if method == TransferMethod.CUDA_IPC:
+            method = TransferMethod.B200_PEER
+        if src is None and dst is None:
+            return {"error": f"neither rank {src_rank} nor rank {dst_rank} is local", "bytes": 0, "blocks": 0}
+        if len(src_blocks) != len(dst_blocks):
+            return {"error": f"Block count mismatch: src={len(src_blocks)}, dst={len(dst_blocks)}",
+                    "bytes": 0, "blocks": 0}
+        if method == TransferMethod.P2P_COPY:
+            if src is None or dst is None:
+                return {"error": "p2p_copy needs both workers in this process", "bytes": 0, "blocks": 0}
+            data = src.extract_kv_blocks(src_blocks)
+            if data.device != dst.device:
+                data = data.to(dst.device, non_blocking=True)
+            dst.write_kv_blocks(dst_blocks, data)
+            torch.cuda.synchronize(dst.device)
+            return {"bytes": data.numel() * data.element_size(), "blocks": len(src_blocks)}
+        if method == TransferMethod.NCCL:
+            if src is not None and dst is not None:
+                return {"error": "nccl transfer needs source and sink in different processes",
+                        "bytes": 0, "blocks": 0}
+            if dst is not None:
+                return dst.p2p_coordinated_transfer_kv(None, src_rank, src_blocks, dst_blocks, timeout=10.0)
+            return src.p2p_send_kv(dst_rank, src_blocks)
+        if method == TransferMethod.B200_PEER:
+            if src is None:
+                return {"bytes": 0, "blocks": len(src_blocks), "passive": True}  # the sink does nothing
+            if dst is not None and dst_rank not in src.peer_pools:
+                # both pools in this process and on this GPU: direct block copy
+                src.pool.copy_blocks(dst.pool, src_blocks, dst_blocks)
+                res = {"bytes": len(src_blocks) * src.pool.block_bytes(), "blocks": len(src_blocks)}
+            else:
+                res = src.p2p_push_kv(dst_rank, src_blocks, dst_blocks)
+            if "error" not in res:
+                torch.cuda.synchronize(src.device)
+                rc, _ = src.ctx.status()
+                if rc != 0:
+                    return {"error": "device reported a bad block id", "bytes": 0, "blocks": 0}
+            return res
+        return {"error": f"transfer method {self.transfer_method.value} is not implemented",
+                "bytes": 0, "blocks": 0}
+
+    async def transfer_kv_cache(self, request_id: str, src_rank: int, dst_rank: int,
+                                src_blocks: List[int], dst_blocks: List[int]) -> bool:
+        """True if the request's blocks were moved (same contract as the reference)."""
+        return self.transfer_kv_cache_sync(request_id, src_rank, dst_rank, src_blocks, dst_blocks)
+
+    def transfer_kv_cache_sync(self, request_id: str, src_rank: int, dst_rank: int,
+                               src_blocks: List[int], dst_blocks: List[int]) -> bool:
+        start = time.perf_counter()
+        try:
+            res = self._run(src_rank, dst_rank, list(src_blocks), list(dst_blocks))
+        except Exception as e:
+            res = {"error": f"{type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+        elapsed = time.perf_counter() - start
+        self.last_result = res
+        if "error" in res:
+            return False
+        if res.get("bytes", 0) == 0 and not res.get("passive"):
+            return False  # the reference treats 0 bytes as a failed transfer
+        self._account(elapsed, res.get("bytes", 0), len(src_blocks))
+        return True
+
+    def transfer_many(self, plan: MigrationPlan) -> bool:
+        """Moves a whole plan: one table per (source, sink) pair.
+
+        Every process that owns a rank named in the plan makes this call. With
+        B200_PEER the sources push and all ranks meet at a barrier; with NCCL
+        each pair runs the staged pipeline.
+        """
+        start = time.perf_counter()
+        method = "peer" if self.transfer_method in (TransferMethod.B200_PEER, TransferMethod.CUDA_IPC) else "nccl"
+        if self.transfer_method not in (TransferMethod.B200_PEER, TransferMethod.CUDA_IPC, TransferMethod.NCCL):
+            ok = all(self.transfer_kv_cache_sync(t.request_id, t.src_rank, t.dst_rank, list(t.src_blocks),
+                                                 list(t.dst_blocks)) for t in plan.transfers)
+            return ok
+        ok = True
+        nbytes = 0
+        for rank, worker in self.worker_registry.items():
+            res = worker.migrate(plan, method=method)
+            self.last_result = res
+            if "error" in res:
+                ok = False
+            else:
+                nbytes += res["bytes"]
+        if ok:
+            self._account(time.perf_counter() - start, nbytes, plan.total_blocks(), count=len(plan.transfers))
+        return ok
+
+    def get_stats(self) -> Dict[str, Any]:
+        return {
+            "transfer_count": self.transfer_count,
+            "total_transfer_time": self.total_transfer_time,
+            "total_bytes_transferred": self.total_bytes_transferred,
+            "avg_transfer_time": self.total_transfer_time / self.transfer_count if self.transfer_count else 0.0,
+        }
+
+    def reset_stats(self) -> None:
+        self.transfer_count = 0
+        self.total_transfer_time = 0.0
+        self.total_bytes_transferred = 0
+
+
+__all__ = ["TransferMethod", "V0KVTransferManager", "MigrationPlan", "Transfer"]

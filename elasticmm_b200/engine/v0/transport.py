@@ -1,0 +1,184 @@
+"""Layer-chunked, double-buffered point-to-point transport of packed KV pages.
+
+The reference moves a request one layer per message, strictly serially:
+gather layer l, blocking send, next layer; the receiver allocates a buffer,
+blocks in recv, then scatters (elasticmm/engine/v0/worker.py:676-682,804-820).
+Here the same per-layer message order is kept but grouped into chunks of
+consecutive layers and pipelined: while chunk c is on the wire, chunk c+1 is
+being packed on the source and chunk c-1 unpacked on the sink. Both sides
+derive the identical chunk schedule from (L, n, page_bytes), so no metadata
+is exchanged beyond what the reference exchanges (the two block-id lists,
+host side).
+
+The functions are written against callables (`pack`, `unpack`, `isend`,
+`irecv`) so the schedule and the buffer-reuse protocol do not depend on where
+the bytes live. On a GPU the callables are KVPool.gather / KVPool.scatter and
+torch.distributed P2P on the NCCL backend, and `Work.wait()` orders streams
+without blocking the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Sequence, Tuple
+
+Chunk = Tuple[int, int]  # (layer_begin, layer_count)
+
+DEFAULT_MESSAGE_BYTES = 64 << 20
+PIPELINE_DEPTH = 2
+
+
+def plan_chunks(num_layers: int, n_blocks: int, page_bytes: int,
+                target_bytes: int = DEFAULT_MESSAGE_BYTES) -> List[Chunk]:
+    """Splits the L layers into consecutive chunks of about `target_bytes` each.
+
+    One layer of n blocks is 2*n*page_bytes on the wire. At least two chunks
+    are produced whenever L >= 2 so that packing and sending can overlap.
+    """
+    if num_layers <= 0 or n_blocks <= 0:
+        return []
+    layer_bytes = 2 * n_blocks * page_bytes
+    per_chunk = max(1, min(num_layers, target_bytes // max(1, layer_bytes)))
+    if num_layers >= 2:
+        per_chunk = min(per_chunk, (num_layers + 1) // 2)
+    return [(b, min(per_chunk, num_layers - b)) for b in range(0, num_layers, per_chunk)]
+
+
+def max_chunk_layers(chunks: Sequence[Chunk]) -> int:
+    return max((c for _, c in chunks), default=0)
+
+
+def pipelined_send(chunks: Sequence[Chunk], buffer_for: Callable[[int, int], object],
+                   pack: Callable[[object, int, int], None],
+                   isend: Callable[[object], object], depth: int = PIPELINE_DEPTH) -> int:
+    """Packs and sends every chunk; returns the number of messages sent.
+
+    `buffer_for(slot, layer_count)` returns the staging buffer of ring slot
+    `slot` shaped for `layer_count` layers. A slot is packed again only after
+    the send that read it has completed.
+    """
+    works: List[object] = []
+    for c, (begin, count) in enumerate(chunks):
+        if c >= depth:
+            works[c - depth].wait()
+        buf = buffer_for(c % depth, count)
+        pack(buf, begin, count)
+        works.append(isend(buf))
+    for w in works[-depth:]:
+        w.wait()
+    return len(works)
+
+
+def pipelined_recv(chunks: Sequence[Chunk], buffer_for: Callable[[int, int], object],
+                   irecv: Callable[[object], object],
+                   unpack: Callable[[object, int, int], None], depth: int = PIPELINE_DEPTH) -> int:
+    """Receives and unpacks every chunk; returns the number of messages received.
+
+    Up to `depth` receives are posted ahead; the receive for chunk c+depth is
+    posted after chunk c has been unpacked from the slot it will land in.
+    """
+    posted: Dict[int, Tuple[object, object]] = {}
+
+    def post(c: int) -> None:
+        buf = buffer_for(c % depth, chunks[c][1])
+        posted[c] = (buf, irecv(buf))
+
+    for c in range(min(depth, len(chunks))):
+        post(c)
+    for c, (begin, count) in enumerate(chunks):
+        buf, work = posted.pop(c)
+        work.wait()
+        unpack(buf, begin, count)
+        if c + depth < len(chunks):
+            post(c + depth)
+    return len(chunks)
+
+
+@dataclass(frozen=True)
+class Transfer:
+    """One request's move: the unit the reference passes to transfer_kv_cache
+    (elasticmm/engine/v0/kv_transfer.py:224-231)."""
+
+    request_id: str
+    src_rank: int
+    dst_rank: int
+    src_blocks: Tuple[int, ...]
+    dst_blocks: Tuple[int, ...]
+
+    def __post_init__(self):
+        if len(self.src_blocks) != len(self.dst_blocks):
+            raise ValueError(
+                f"Block count mismatch: src={len(self.src_blocks)}, dst={len(self.dst_blocks)}")
+
+
+class MigrationPlan:
+    """All transfers of one role switch, grouped by (source, sink) pair.
+
+    The reference migrates a GPU's requests one awaited RPC at a time
+    (elasticmm/engine/v0/backend.py:674-718). Grouping the same tuples by
+    pair lets each pair move as one long table: per pair the block lists are
+    concatenated in plan order, which is also the page order on the wire.
+    """
+
+    def __init__(self, transfers: Sequence[Transfer] = ()):
+        self.transfers: List[Transfer] = []
+        for t in transfers:
+            self.add(t)
+
+    def add(self, t: Transfer) -> None:
+        if t.src_rank == t.dst_rank:
+            raise ValueError(f"{t.request_id}: source and sink rank are both {t.src_rank}")
+        self.transfers.append(t)
+
+    def pairs(self) -> List[Tuple[int, int]]:
+        """(src, dst) pairs in a fixed order every rank agrees on."""
+        return sorted({(t.src_rank, t.dst_rank) for t in self.transfers})
+
+    def ordered_pairs(self) -> List[Tuple[int, int]]:
+        """Pairs in the order every rank serves them.
+
+        Source number i starts at sink number i and walks the sinks cyclically,
+        so concurrent sources meet different sinks first. Sorting all pairs by
+        (step, source) gives one total order; a rank that serves its own pairs
+        in that order can never be part of a circular wait, because the
+        globally first unfinished pair is first for both of its ends.
+        """
+        pairs = self.pairs()
+        sources = sorted({s for s, _ in pairs})
+        sinks = sorted({d for _, d in pairs})
+        m = len(sinks)
+        step = lambda sd: (sinks.index(sd[1]) - sources.index(sd[0])) % m
+        return sorted(pairs, key=lambda sd: (step(sd), sd[0], sd[1]))
+
+    def tables(self, src_rank: int, dst_rank: int) -> Tuple[List[int], List[int]]:
+        """Concatenated (src_blocks, dst_blocks) of one pair, in plan order."""
+        src: List[int] = []
+        dst: List[int] = []
+        for t in self.transfers:
+            if t.src_rank == src_rank and t.dst_rank == dst_rank:
+                src += t.src_blocks
+                dst += t.dst_blocks
+        return src, dst
+
+    def outgoing(self, rank: int) -> List[int]:
+        return [d for s, d in self.pairs() if s == rank]
+
+    def incoming(self, rank: int) -> List[int]:
+        return [s for s, d in self.pairs() if d == rank]
+
+    def total_blocks(self) -> int:
+        return sum(len(t.src_blocks) for t in self.transfers)
+
+    def validate(self, num_blocks_of_rank: Callable[[int], int]) -> None:
+        """Range-checks every id and rejects a destination block used twice."""
+        seen_dst: Dict[int, set] = {}
+        for t in self.transfers:
+            nb_s, nb_d = num_blocks_of_rank(t.src_rank), num_blocks_of_rank(t.dst_rank)
+            if any(b < 0 or b >= nb_s for b in t.src_blocks):
+                raise ValueError(f"{t.request_id}: source block outside [0, {nb_s})")
+            if any(b < 0 or b >= nb_d for b in t.dst_blocks):
+                raise ValueError(f"{t.request_id}: destination block outside [0, {nb_d})")
+            used = seen_dst.setdefault(t.dst_rank, set())
+            for b in t.dst_blocks:
+                if b in used:
+                    raise ValueError(f"{t.request_id}: destination block {b} on rank {t.dst_rank} assigned twice")
+                used.add(b)

@@ -1,0 +1,425 @@
+"""The worker's KV data plane, with the reference's method names.
+
+Each public method keeps the name, argument meaning, return shape and error
+convention of the V0Worker method it stands in for
+(elasticmm/engine/v0/worker.py:478-1005); the device work underneath is the
+CUDA library (one launch for all layers instead of one torch indexing kernel
+per layer). In the reference this class is a Ray actor; here it is a plain
+class owned by one process bound to one GPU, and the `@ray.remote` decoration
+is left to the integrator.
+
+Data-path errors are returned as {"error": ..., "bytes": 0, "blocks": 0}
+rather than raised, precondition failures raise ValueError / RuntimeError
+(elasticmm/engine/v0/worker.py:686-691,766-776).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ... import _lib
+from ...kv_pool import Context, KVPool, get_context
+from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_recv,
+                        pipelined_send, PIPELINE_DEPTH)
+from .utils import EngineStage
+
+_DTYPES = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
+           "float32": torch.float32, "float": torch.float32}
+
+
+class V0Worker:
+    """One GPU's KV pool plus the operations that move its blocks."""
+
+    def __init__(
+        self,
+        worker_id: int = 0,
+        stage: EngineStage = EngineStage.PREFILL,
+        block_size: int = 16,
+        dtype: str = "float16",
+        device: Optional[torch.device] = None,
+        global_rank: Optional[int] = None,
+        world_size: Optional[int] = None,
+        nccl_init_method: Optional[str] = None,
+        kv_cache: Optional[Sequence[torch.Tensor]] = None,
+    ):
+        if not torch.cuda.is_available():
+            raise RuntimeError("V0Worker needs a CUDA device; the KV data plane has no CPU path")
+        self.worker_id = worker_id
+        self.stage = stage
+        self.original_role = stage
+        self.current_role = stage
+        self.block_size = block_size
+        self.dtype = dtype
+        self.global_rank = global_rank
+        self.nccl_world_size = world_size
+        self.nccl_init_method = nccl_init_method
+        self.nccl_pg_initialized = False
+        self.process_group = None
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self.ctx: Context = get_context(self.device)
+        self.kv_cache: Optional[List[torch.Tensor]] = None
+        self.kv_swap: Optional[List[torch.Tensor]] = None
+        self.pool: Optional[KVPool] = None
+        self.swap_pool: Optional[KVPool] = None
+        self.peer_pools: Dict[int, KVPool] = {}
+        self.swap_in_stream = torch.cuda.Stream(self.device)
+        self.swap_out_stream = torch.cuda.Stream(self.device)
+        self.swap_event_table: Dict[str, torch.cuda.Event] = {}
+        self.latest_swap_in_event: Optional[torch.cuda.Event] = None
+        self.latest_swap_out_event: Optional[torch.cuda.Event] = None
+        self._xfer_stream = torch.cuda.Stream(self.device)
+        self._staging: Optional[torch.Tensor] = None  # flat byte ring for the staged NCCL path
+        if kv_cache is not None:
+            self.bind_kv_cache(kv_cache)
+
+    # -- pool set-up -----------------------------------------------------------
+    def init_kvcache(self, num_gpu_blocks: int, num_layers: int, num_kv_heads: int, head_size: int,
+                     num_cpu_blocks: int = 0) -> None:
+        """Allocates the pool in the reference layout: L tensors [2, NB, BS, H, D].
+
+        In the reference the tensors come from vLLM's CacheEngine
+        (elasticmm/engine/v0/worker.py:369-394); use bind_kv_cache to adopt those.
+        """
+        dt = _DTYPES[self.dtype]
+        shape = (2, num_gpu_blocks, self.block_size, num_kv_heads, head_size)
+        self.bind_kv_cache([torch.empty(shape, dtype=dt, device=self.device) for _ in range(num_layers)])
+        if num_cpu_blocks > 0:
+            cshape = (2, num_cpu_blocks, self.block_size, num_kv_heads, head_size)
+            self.bind_kv_swap([torch.empty(cshape, dtype=dt).pin_memory() for _ in range(num_layers)])
+
+    def bind_kv_cache(self, kv_cache: Sequence[torch.Tensor]) -> None:
+        """Adopts an existing list of per-layer pool tensors (not copied)."""
+        self.kv_cache = list(kv_cache)
+        self.pool = KVPool(self.kv_cache, self.ctx)
+
+    def bind_kv_swap(self, kv_swap: Sequence[torch.Tensor]) -> None:
+        """Adopts a pinned host pool with the GPU pool's page geometry."""
+        self.kv_swap = list(kv_swap)
+        self.swap_pool = KVPool(self.kv_swap, self.ctx)
+
+    def _require_pool(self) -> KVPool:
+        if self.pool is None:
+            raise RuntimeError("KV cache not initialized")
+        return self.pool
+
+    def get_stage(self) -> EngineStage:
+        return self.stage
+
+    def set_stage(self, stage: EngineStage) -> None:
+        self.stage = stage
+
+    def switch_role(self, new_stage: EngineStage) -> bool:
+        """Logical role change; the pool and the global rank stay
+        (elasticmm/engine/v0/worker.py:1066-1131)."""
+        self.stage = new_stage
+        self.current_role = new_stage
+        return True
+
+    # -- gather / scatter (elasticmm/engine/v0/worker.py:578-647) --------------
+    def extract_kv_blocks(self, block_indices: List[int]) -> torch.Tensor:
+        """Returns [num_layers, 2, num_blocks, block_size, num_heads, head_size]."""
+        return self._require_pool().gather(block_indices)
+
+    def write_kv_blocks(self, block_indices: List[int], kv_data: torch.Tensor) -> None:
+        pool = self._require_pool()
+        assert kv_data.shape[2] == len(block_indices), (
+            f"Block count mismatch: {kv_data.shape[2]} vs {len(block_indices)}")
+        pool.scatter(block_indices, kv_data)
+
+    def get_kv_cache_layout(self) -> Dict[str, Any]:
+        if not self.kv_cache:
+            return {}
+        pool = self._require_pool()
+        return {
+            "num_layers": pool.num_layers,
+            "block_size": pool.block_size,
+            "num_heads": pool.num_kv_heads,
+            "head_size": pool.head_size,
+            "dtype": str(pool.dtype).split(".")[-1],
+        }
+
+    # -- append and compaction (no counterpart in the reference's own code) ----
+    def reshape_and_cache(self, key: torch.Tensor, value: torch.Tensor,
+                          slot_mapping: torch.Tensor, layer: int) -> None:
+        """Writes one layer's new-token K/V rows at their slots; slot < 0 skipped."""
+        self._require_pool().append(layer, key, value, slot_mapping)
+
+    def reshape_and_cache_all_layers(self, key: torch.Tensor, value: torch.Tensor,
+                                     slot_mapping: torch.Tensor) -> None:
+        """Same for all layers at once; key/value are [L, T, H, D]."""
+        self._require_pool().append_all_layers(key, value, slot_mapping)
+
+    def compact_blocks(self, move_src: Sequence[int], move_dst: Sequence[int]) -> Dict[str, Any]:
+        """Executes a compaction plan (V0BlockManager.compact) inside the pool."""
+        pool = self._require_pool()
+        try:
+            pool.copy_blocks(pool, move_src, move_dst)
+        except _lib.EmmError as e:
+            return {"error": str(e), "bytes": 0, "blocks": 0}
+        return {"bytes": len(move_src) * pool.block_bytes(), "blocks": len(move_src)}
+
+    # -- GPU <-> CPU swap (elasticmm/engine/v0/worker.py:478-526) ---------------
+    def swap_blocks(self, request_ids: List[str], source_block_ids: List[int],
+                    target_block_ids: List[int], is_swap_in: bool) -> None:
+        """Copies blocks between the pinned host pool and the GPU pool.
+
+        If is_swap_in, host block source_block_ids[i] goes to GPU block
+        target_block_ids[i]; otherwise the other way. One kernel launch on the
+        swap stream; a request's later swap waits for its earlier one.
+        """
+        pool = self._require_pool()
+        if self.swap_pool is None:
+            raise RuntimeError("CPU swap pool not initialized")
+        stream = self.swap_in_stream if is_swap_in else self.swap_out_stream
+        for rid in request_ids:
+            prev = self.swap_event_table.get(rid)
+            if prev is not None:
+                stream.wait_event(prev)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            if is_swap_in:
+                self.swap_pool.copy_blocks(pool, source_block_ids, target_block_ids)
+            else:
+                pool.copy_blocks(self.swap_pool, source_block_ids, target_block_ids)
+            event = torch.cuda.Event()
+            event.record(stream)
+        for rid in request_ids:
+            self.swap_event_table[rid] = event
+        if is_swap_in:
+            self.latest_swap_in_event = event
+        else:
+            self.latest_swap_out_event = event
+
+    def wait_for_all_swap_in(self) -> None:
+        if self.latest_swap_in_event is not None:
+            self.latest_swap_in_event.synchronize()
+
+    def wait_for_all_swap_out(self) -> None:
+        if self.latest_swap_out_event is not None:
+            self.latest_swap_out_event.synchronize()
+
+    def clear_request_resource(self, request_id: str) -> None:
+        self.swap_event_table.pop(request_id, None)
+
+    # -- process group ---------------------------------------------------------
+    def init_global_nccl(self, process_group=None) -> bool:
+        """True when a process group is ready for P2P transfer
+        (elasticmm/engine/v0/worker.py:649-659). The group itself is created by
+        the launcher (torchrun-style environment or init_process_group with the
+        coordinator's init method); NVSwitch needs none of the PCIe-era NCCL
+        environment overrides the reference sets."""
+        if not dist.is_available() or not dist.is_initialized():
+            return False
+        self.process_group = process_group
+        self.nccl_pg_initialized = True
+        if self.global_rank is None:
+            self.global_rank = dist.get_rank()
+        return True
+
+    def get_global_rank(self) -> int:
+        return self.global_rank if self.global_rank is not None else -1
+
+    # -- staged NCCL transfer (elasticmm/engine/v0/worker.py:665-871) -----------
+    def _staging_views(self, pool: KVPool, n: int, chunks) -> List[torch.Tensor]:
+        need = pool.packed_bytes(n, max_chunk_layers(chunks))
+        total = need * PIPELINE_DEPTH
+        if self._staging is None or self._staging.numel() < total:
+            self._staging = torch.empty(total, dtype=torch.uint8, device=self.device)
+        return [self._staging[i * need:(i + 1) * need] for i in range(PIPELINE_DEPTH)]
+
+    def _buffer_for(self, pool: KVPool, n: int, slots: List[torch.Tensor]):
+        def buffer_for(slot: int, layer_count: int) -> torch.Tensor:
+            flat = slots[slot][: pool.packed_bytes(n, layer_count)].view(pool.dtype)
+            return pool._logical(flat.view(pool.packed_shape(n, layer_count)))
+        return buffer_for
+
+    def p2p_send_kv(self, dst_rank: int, block_indices: List[int]) -> Dict[str, Any]:
+        """Packs the blocks chunk by chunk and sends them to `dst_rank`.
+
+        Packing of chunk c+1 overlaps the send of chunk c. The call returns
+        after the device has finished, as the reference does.
+        """
+        if not self.nccl_pg_initialized:
+            return {"error": "Global NCCL not initialized", "bytes": 0, "blocks": 0}
+        try:
+            pool = self._require_pool()
+            n = len(block_indices)
+            if n == 0:
+                return {"bytes": 0, "blocks": 0}
+            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices)))
+            chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
+            slots = self._staging_views(pool, n, chunks)
+            main = torch.cuda.current_stream(self.device)
+            self._xfer_stream.wait_stream(main)
+            with torch.cuda.stream(self._xfer_stream):
+                pipelined_send(
+                    chunks, self._buffer_for(pool, n, slots),
+                    pack=lambda buf, b, c: pool.gather(ids, out=buf, layer_begin=b, layer_count=c),
+                    isend=lambda buf: dist.isend(pool._logical(buf), dst=dst_rank, group=self.process_group),
+                )
+            main.wait_stream(self._xfer_stream)
+            torch.cuda.synchronize(self.device)
+            rc, detail = self.ctx.status()
+            if rc != _lib.OK:
+                return {"error": f"send failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+            return {"bytes": pool.packed_bytes(n), "blocks": n}
+        except Exception as e:  # data-path errors are reported, not raised
+            return {"error": f"NCCL send failed: {type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+
+    def p2p_recv_kv(self, src_rank: int, block_indices: List[int]) -> Dict[str, Any]:
+        """Receives chunk by chunk and scatters into `block_indices`."""
+        if not self.nccl_pg_initialized:
+            return {"error": "Global NCCL not initialized", "bytes": 0, "blocks": 0}
+        try:
+            pool = self._require_pool()
+            n = len(block_indices)
+            if n == 0:
+                return {"bytes": 0, "blocks": 0}
+            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices), unique=True))
+            chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
+            slots = self._staging_views(pool, n, chunks)
+            main = torch.cuda.current_stream(self.device)
+            self._xfer_stream.wait_stream(main)
+            with torch.cuda.stream(self._xfer_stream):
+                pipelined_recv(
+                    chunks, self._buffer_for(pool, n, slots),
+                    irecv=lambda buf: dist.irecv(pool._logical(buf), src=src_rank, group=self.process_group),
+                    unpack=lambda buf, b, c: pool.scatter(ids, buf, layer_begin=b, layer_count=c),
+                )
+            main.wait_stream(self._xfer_stream)
+            torch.cuda.synchronize(self.device)
+            rc, detail = self.ctx.status()
+            if rc != _lib.OK:
+                return {"error": f"recv failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+            return {"bytes": pool.packed_bytes(n), "blocks": n}
+        except Exception as e:
+            return {"error": f"NCCL recv failed: {type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+
+    def p2p_coordinated_transfer_kv(self, src_worker_ref: Any, src_rank: int, src_blocks: List[int],
+                                    dst_blocks: List[int], timeout: float = 10.0) -> Dict[str, Any]:
+        """Called on the DESTINATION worker: triggers the source's send, then receives.
+
+        `src_worker_ref` is an actor-style handle whose
+        `p2p_send_kv.remote(dst_rank, blocks)` starts the send in the source's
+        process and returns a future with `.result(timeout)`-like access via
+        `get()`; pass None when the source process calls p2p_send_kv itself
+        (one process per GPU, both sides following the same plan).
+        """
+        if not self.nccl_pg_initialized:
+            raise RuntimeError("Destination worker: Global NCCL not initialized")
+        if len(src_blocks) != len(dst_blocks):
+            raise ValueError(f"Block count mismatch: src={len(src_blocks)}, dst={len(dst_blocks)}")
+        if len(src_blocks) == 0:
+            return {"bytes": 0, "blocks": 0, "error": "No blocks to transfer"}
+        world = dist.get_world_size(self.process_group)
+        if src_rank < 0 or src_rank >= world:
+            raise ValueError(f"Invalid src_rank: {src_rank} (world_size={world})")
+        start = time.time()
+        send_future = None
+        if src_worker_ref is not None:
+            send_future = src_worker_ref.p2p_send_kv.remote(dist.get_rank(self.process_group), src_blocks)
+        result = self.p2p_recv_kv(src_rank, dst_blocks)
+        elapsed = time.time() - start
+        if "error" in result:
+            result["elapsed"] = elapsed
+            return result
+        if elapsed > timeout:
+            return {"error": f"Transfer timeout after {timeout}s", "bytes": 0, "blocks": 0, "elapsed": elapsed}
+        if send_future is not None:
+            try:
+                send_result = send_future.get(timeout=1.0) if hasattr(send_future, "get") else send_future
+            except Exception as send_err:
+                return {"error": f"Send failed: {type(send_err).__name__}: {send_err}", "bytes": 0,
+                        "blocks": 0, "elapsed": elapsed}
+            if isinstance(send_result, dict) and "error" in send_result:
+                return {"error": f"Send error: {send_result['error']}", "bytes": 0, "blocks": 0,
+                        "elapsed": elapsed}
+        return {"bytes": result["bytes"], "blocks": len(dst_blocks), "elapsed": elapsed,
+                "method": "coordinated_single_call"}
+
+    # -- direct peer stores (the slot the reference reserves for a CUDA-IPC
+    #    extension, elasticmm/engine/v0/kv_transfer.py:303-331) ----------------
+    def get_ipc_handles(self) -> List[Tuple[bytes, int]]:
+        """(handle, offset) per layer for other processes on this node
+        (the reference's stub returns [], elasticmm/engine/v0/worker.py:415-437)."""
+        pool = self._require_pool()
+        return [self.ctx.ipc_export(t) for t in pool.layers]
+
+    def get_pool_desc(self) -> Dict[str, int]:
+        d = self._require_pool().desc
+        return {name: int(getattr(d, name)) for name, _ in d._fields_}
+
+    def attach_peer_pool(self, rank: int, handles: Sequence[Tuple[bytes, int]], desc: Dict[str, int],
+                         dtype: Optional[torch.dtype] = None) -> None:
+        """Maps the pool of the worker with global rank `rank` into this process."""
+        ptrs = [self.ctx.ipc_open(h, off) for h, off in handles]
+        pd = _lib.PoolDesc(**desc)
+        self.peer_pools[rank] = KVPool.from_pointers(self.ctx, pd, ptrs, dtype or self._require_pool().dtype)
+
+    def p2p_push_kv(self, dst_rank: int, src_blocks: List[int], dst_blocks: List[int]) -> Dict[str, Any]:
+        """Copies blocks straight into the mapped pool of `dst_rank`: one kernel,
+        local loads, stores over NVLink, no staging buffer and no NCCL call.
+        Asynchronous on the current stream; the caller orders the sink's first
+        read after this stream's completion (an event wait, a barrier, or any
+        stream-ordered message to the sink)."""
+        if dst_rank not in self.peer_pools:
+            return {"error": f"pool of rank {dst_rank} is not mapped", "bytes": 0, "blocks": 0}
+        if len(src_blocks) != len(dst_blocks):
+            raise ValueError(f"Block count mismatch: src={len(src_blocks)}, dst={len(dst_blocks)}")
+        pool = self._require_pool()
+        try:
+            pool.copy_blocks(self.peer_pools[dst_rank], src_blocks, dst_blocks)
+        except _lib.EmmError as e:
+            return {"error": str(e), "bytes": 0, "blocks": 0}
+        return {"bytes": len(src_blocks) * pool.block_bytes(), "blocks": len(src_blocks)}
+
+    # -- plan-level migration -----------------------------------------------------
+    def migrate(self, plan: MigrationPlan, method: str = "peer") -> Dict[str, Any]:
+        """Runs this rank's part of a migration plan; every rank in the plan calls it.
+
+        method "peer": one direct-store launch per sink, then a barrier.
+        method "nccl": per pair, the staged pipeline of p2p_send_kv / p2p_recv_kv;
+        every rank walks the pairs in the plan's one global order (sources
+        start at different sinks), which rules out a circular wait.
+        """
+        rank = self.get_global_rank()
+        pool = self._require_pool()
+        moved = 0
+        if method == "peer":
+            for dst in plan.outgoing(rank):
+                src_ids, dst_ids = plan.tables(rank, dst)
+                res = self.p2p_push_kv(dst, src_ids, dst_ids)
+                if "error" in res:
+                    return res
+                moved += res["blocks"]
+            torch.cuda.synchronize(self.device)
+            rc, _ = self.ctx.status()
+            dist.barrier(group=self.process_group)
+            if rc != _lib.OK:
+                return {"error": f"push failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+        elif method == "nccl":
+            if plan.outgoing(rank) and plan.incoming(rank):
+                return {"error": "nccl migration needs each rank to be a pure source or a pure sink; "
+                                 "use the peer method for exchanges", "bytes": 0, "blocks": 0}
+            for src, dst in plan.ordered_pairs():
+                if src == rank:
+                    res = self.p2p_send_kv(dst, plan.tables(src, dst)[0])
+                elif dst == rank:
+                    res = self.p2p_recv_kv(src, plan.tables(src, dst)[1])
+                else:
+                    continue
+                if "error" in res:
+                    return res
+                moved += res["blocks"]
+        else:
+            raise ValueError(f"unknown migration method {method!r}")
+        return {"bytes": moved * pool.block_bytes(), "blocks": moved}
+
+
+def _lib_ids(ids):
+    from ...kv_pool import _as_host_ids
+    return _as_host_ids(ids)

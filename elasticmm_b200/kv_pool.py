@@ -1,0 +1,412 @@
+"""Python face of the C ABI: device contexts and paged KV pools.
+
+`Context` wraps one `emm_ctx` (one per process and GPU); `KVPool` wraps one
+`emm_pool` built from the tensors a worker already owns. torch is used for
+device memory and streams only; every byte of KV data is moved by the CUDA
+kernels in libemm_kv.so. Nothing here computes on the CPU, and nothing falls
+back to torch indexing when the library or a GPU is missing.
+
+Pool tensors follow the reference: a list of L tensors, logical shape
+[2, NB, BS, H, D] (elasticmm/engine/v0/worker.py:388-394,593-594). The byte
+strides are read off each tensor, so a head-major pool is passed as the
+permuted view `t.permute(0, 1, 3, 2, 4)` of a [2, NB, H, BS, D] allocation
+and a single 6-D tensor [L, 2, NB, BS, H, D]
+(elasticmm/engine/v0/nccl_transfer.py:215) as `list(t.unbind(0))`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from . import _lib
+
+IdList = Union[Sequence[int], np.ndarray, torch.Tensor]
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class Context:
+    """One emm_ctx: device status word, id staging ring, kernel options."""
+
+    def __init__(self, device: Union[int, torch.device]):
+        if not torch.cuda.is_available():
+            raise RuntimeError("elasticmm_b200 needs a CUDA device; there is no CPU path")
+        dev = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        if dev.type != "cuda":
+            raise ValueError(f"KV pools live on CUDA devices, got {dev}")
+        index = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.device = torch.device("cuda", index)
+        self._lib = _lib.load()
+        torch.cuda.init()
+        with torch.cuda.device(self.device):
+            torch.zeros(1, device=self.device)  # make sure the primary context exists
+            handle = C.c_void_p()
+            _lib.check(self._lib.emm_ctx_create(index, C.byref(handle)))
+        self._h = handle
+
+    # -- options ---------------------------------------------------------
+    def set_option(self, option: int, value: int) -> None:
+        _lib.check(self._lib.emm_ctx_set_option(self._h, option, int(value)))
+
+    def get_option(self, option: int) -> int:
+        out = C.c_int64()
+        _lib.check(self._lib.emm_ctx_get_option(self._h, option, C.byref(out)))
+        return out.value
+
+    def configure(self, *, variant: Optional[int] = None, chunk_bytes: Optional[int] = None,
+                  stages: Optional[int] = None, warps: Optional[int] = None,
+                  ctas_per_sm: Optional[int] = None, ldg_unroll: Optional[int] = None,
+                  max_ctas: Optional[int] = None) -> None:
+        """Sets copy-kernel options; None leaves an option as it is."""
+        pairs = [
+            (_lib.OPT_COPY_VARIANT, variant), (_lib.OPT_CHUNK_BYTES, chunk_bytes),
+            (_lib.OPT_STAGES, stages), (_lib.OPT_WARPS, warps),
+            (_lib.OPT_CTAS_PER_SM, ctas_per_sm), (_lib.OPT_LDG_UNROLL, ldg_unroll),
+            (_lib.OPT_MAX_CTAS, max_ctas),
+        ]
+        for opt, val in pairs:
+            if val is not None:
+                self.set_option(opt, val)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.emm_ctx_launch_count(self._h))
+
+    def status(self) -> Tuple[int, int]:
+        """Synchronises the current stream; returns (status, detail) and clears it."""
+        detail = C.c_int64()
+        rc = self._lib.emm_ctx_status(self._h, C.c_void_p(_stream_ptr(self.device)), C.byref(detail))
+        return rc, detail.value
+
+    def check_status(self) -> None:
+        """Raises EmmError if a kernel recorded a bad id, slot or a timeout."""
+        rc, _ = self.status()
+        _lib.check(rc)
+
+    # -- peer mapping ------------------------------------------------------
+    def ipc_export(self, tensor: torch.Tensor) -> Tuple[bytes, int]:
+        """(handle, offset) naming `tensor`'s storage for another process."""
+        buf = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        off = C.c_uint64()
+        _lib.check(self._lib.emm_ipc_export(self._h, C.c_void_p(tensor.data_ptr()), buf, C.byref(off)))
+        return bytes(buf.raw), off.value
+
+    def ipc_open(self, handle: bytes, offset: int) -> int:
+        """Maps a peer allocation; returns the device address in this process."""
+        out = C.c_void_p()
+        _lib.check(self._lib.emm_ipc_open(self._h, handle, C.c_uint64(offset), C.byref(out)))
+        return int(out.value)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            self._lib.emm_ctx_destroy(self._h)
+            self._h = None
+
+
+_contexts: Dict[int, Context] = {}
+
+
+def get_context(device: Union[int, torch.device, None] = None) -> Context:
+    """The process-wide Context of a device (created on first use)."""
+    if device is None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("elasticmm_b200 needs a CUDA device; there is no CPU path")
+        index = torch.cuda.current_device()
+    elif isinstance(device, int):
+        index = device
+    else:
+        d = torch.device(device)
+        index = d.index if d.index is not None else torch.cuda.current_device()
+    ctx = _contexts.get(index)
+    if ctx is None:
+        ctx = Context(index)
+        _contexts[index] = ctx
+    return ctx
+
+
+def _as_host_ids(ids: IdList) -> np.ndarray:
+    if isinstance(ids, torch.Tensor):
+        ids = ids.detach().cpu().numpy()
+    arr = np.ascontiguousarray(ids, dtype=np.int64)
+    if arr.ndim != 1:
+        raise ValueError("block ids must be a flat list")
+    return arr
+
+
+class KVPool:
+    """A paged KV pool known to the library.
+
+    `layers` are the L per-layer tensors of logical shape [2, NB, BS, H, D]
+    with the innermost dimension contiguous. For a pool that is not torch
+    memory (a peer GPU's pool mapped by Context.ipc_open, a pinned host pool)
+    use `KVPool.from_pointers`.
+    """
+
+    def __init__(self, layers: Sequence[torch.Tensor], ctx: Optional[Context] = None):
+        layers = list(layers)
+        if not layers:
+            raise ValueError("a pool needs at least one layer tensor")
+        first = layers[0]
+        if first.dim() != 5 or first.shape[0] != 2:
+            raise ValueError(f"layer tensors must be [2, NB, BS, H, D], got {tuple(first.shape)}")
+        for t in layers:
+            if t.shape != first.shape or t.dtype != first.dtype or t.stride() != first.stride():
+                raise ValueError("all layer tensors must share shape, dtype and strides")
+            if t.stride(4) != 1:
+                raise ValueError("head_dim must be contiguous")
+        device = first.device
+        if device.type == "cuda":
+            self.ctx = ctx or get_context(device)
+        else:
+            if ctx is None or not first.is_pinned():
+                raise ValueError("a host pool must be pinned and needs an explicit Context")
+            self.ctx = ctx
+        e = first.element_size()
+        desc = _lib.PoolDesc(
+            num_layers=len(layers), num_blocks=first.shape[1], block_size=first.shape[2],
+            num_kv_heads=first.shape[3], head_size=first.shape[4], elem_size=e,
+            plane_stride=first.stride(0) * e, block_stride=first.stride(1) * e,
+            token_stride=first.stride(2) * e, head_stride=first.stride(3) * e,
+        )
+        self._layers = layers  # keeps the memory alive
+        self.dtype = first.dtype
+        self._init_handle(desc, [t.data_ptr() for t in layers])
+
+    @classmethod
+    def from_pointers(cls, ctx: Context, desc: "_lib.PoolDesc", layer_ptrs: Sequence[int],
+                      dtype: torch.dtype) -> "KVPool":
+        """A pool over raw addresses (peer-mapped or host-pinned memory)."""
+        self = cls.__new__(cls)
+        self.ctx = ctx
+        self._layers = None
+        self.dtype = dtype
+        self._init_handle(desc, list(layer_ptrs))
+        return self
+
+    def _init_handle(self, desc: "_lib.PoolDesc", ptrs: List[int]) -> None:
+        lib = self.ctx._lib
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        handle = C.c_void_p()
+        _lib.check(lib.emm_pool_create(self.ctx._h, C.byref(desc), arr, C.byref(handle)))
+        self._h = handle
+        self.desc = desc
+        self.layer_ptrs = ptrs
+        self.num_layers = desc.num_layers
+        self.num_blocks = desc.num_blocks
+        self.block_size = desc.block_size
+        self.num_kv_heads = desc.num_kv_heads
+        self.head_size = desc.head_size
+        self.elem_size = desc.elem_size
+        self.page_bytes = int(lib.emm_pool_page_bytes(handle))
+        # head-major pages: tokens step by D, heads by BS*D
+        self.head_major = (desc.num_kv_heads > 1 and desc.block_size > 1
+                           and desc.token_stride == desc.head_size * desc.elem_size)
+
+    # -- helpers ---------------------------------------------------------
+    @property
+    def device(self) -> torch.device:
+        return self.ctx.device
+
+    @property
+    def layers(self) -> Optional[List[torch.Tensor]]:
+        return self._layers
+
+    def block_bytes(self) -> int:
+        """Bytes of one block over all layers, K and V."""
+        return 2 * self.num_layers * self.page_bytes
+
+    def packed_bytes(self, n: int, layer_count: Optional[int] = None) -> int:
+        lc = self.num_layers if layer_count is None else layer_count
+        return lc * 2 * n * self.page_bytes
+
+    def packed_shape(self, n: int, layer_count: Optional[int] = None) -> Tuple[int, ...]:
+        lc = self.num_layers if layer_count is None else layer_count
+        if self.head_major:
+            return (lc, 2, n, self.num_kv_heads, self.block_size, self.head_size)
+        return (lc, 2, n, self.block_size, self.num_kv_heads, self.head_size)
+
+    def _logical(self, packed: torch.Tensor) -> torch.Tensor:
+        """[.., n, BS, H, D] view of a packed buffer, whatever the page order."""
+        return packed.permute(0, 1, 2, 4, 3, 5) if self.head_major else packed
+
+    def new_packed(self, n: int, layer_count: Optional[int] = None) -> torch.Tensor:
+        """An uninitialised packed buffer; logical shape [L, 2, n, BS, H, D]."""
+        return self._logical(torch.empty(self.packed_shape(n, layer_count), dtype=self.dtype,
+                                         device=self.device))
+
+    def _packed_ptr(self, packed: torch.Tensor, n: int, layer_count: int) -> Tuple[int, int]:
+        want = (layer_count, 2, n, self.block_size, self.num_kv_heads, self.head_size)
+        if tuple(packed.shape) != want:
+            raise ValueError(f"packed tensor has shape {tuple(packed.shape)}, expected {want}")
+        if packed.dtype != self.dtype:
+            raise ValueError(f"packed tensor dtype {packed.dtype} differs from pool dtype {self.dtype}")
+        if packed.device != self.device:
+            raise ValueError(f"packed tensor on {packed.device}, pool on {self.device}")
+        phys = self._logical(packed)  # permute is its own inverse here
+        if not phys.is_contiguous():
+            raise ValueError("packed tensor must be contiguous in the pool's page order")
+        return phys.data_ptr(), phys.numel() * phys.element_size()
+
+    def upload_ids(self, ids: IdList) -> torch.Tensor:
+        """int32 device table from a host list (stream ordered, pinned staging)."""
+        host = torch.from_numpy(_as_host_ids(ids).astype(np.int32)).pin_memory()
+        return host.to(self.device, non_blocking=True)
+
+    @staticmethod
+    def _check_table(t: torch.Tensor, device: torch.device) -> None:
+        if t.dtype != torch.int32 or t.dim() != 1 or not t.is_contiguous() or t.device != device:
+            raise ValueError("device id tables must be contiguous 1-D int32 tensors on the pool's device")
+
+    # -- whole-block movement -----------------------------------------------
+    def gather(self, ids: IdList, out: Optional[torch.Tensor] = None,
+               layer_begin: int = 0, layer_count: Optional[int] = None) -> torch.Tensor:
+        """packed[l, p, i] = pool[l][p, ids[i]]; one launch for all layers.
+
+        `ids` is a host list (range checked on the host, uploaded on the
+        current stream) or an int32 device tensor (checked by the kernel).
+        """
+        lc = self.num_layers - layer_begin if layer_count is None else layer_count
+        lib = self.ctx._lib
+        st = C.c_void_p(_stream_ptr(self.device))
+        if isinstance(ids, torch.Tensor) and ids.is_cuda:
+            self._check_table(ids, self.device)
+            n = ids.numel()
+            out = self.new_packed(n, lc) if out is None else out
+            ptr, nbytes = self._packed_ptr(out, n, lc)
+            _lib.check(lib.emm_gather_layers(self._h, layer_begin, lc, C.c_void_p(ids.data_ptr()), n,
+                                             C.c_void_p(ptr), nbytes, st))
+            return out
+        host = _as_host_ids(ids)
+        n = host.shape[0]
+        if layer_begin != 0 or lc != self.num_layers:
+            return self.gather(self.upload_ids(self._validated(host)), out, layer_begin, lc)
+        out = self.new_packed(n, lc) if out is None else out
+        ptr, nbytes = self._packed_ptr(out, n, lc)
+        _lib.check(lib.emm_gather_h(self._h, host.ctypes.data_as(C.c_void_p), n, C.c_void_p(ptr), nbytes, st))
+        return out
+
+    def scatter(self, ids: IdList, packed: torch.Tensor,
+                layer_begin: int = 0, layer_count: Optional[int] = None) -> None:
+        """pool[l][p, ids[i]] = packed[l, p, i]; one launch for all layers."""
+        lc = self.num_layers - layer_begin if layer_count is None else layer_count
+        lib = self.ctx._lib
+        st = C.c_void_p(_stream_ptr(self.device))
+        if isinstance(ids, torch.Tensor) and ids.is_cuda:
+            self._check_table(ids, self.device)
+            n = ids.numel()
+            ptr, nbytes = self._packed_ptr(packed, n, lc)
+            _lib.check(lib.emm_scatter_layers(self._h, layer_begin, lc, C.c_void_p(ids.data_ptr()), n,
+                                              C.c_void_p(ptr), nbytes, st))
+            return
+        host = _as_host_ids(ids)
+        n = host.shape[0]
+        if layer_begin != 0 or lc != self.num_layers:
+            host = self._validated(host, unique=True)
+            return self.scatter(self.upload_ids(host), packed, layer_begin, lc)
+        ptr, nbytes = self._packed_ptr(packed, n, lc)
+        _lib.check(lib.emm_scatter_h(self._h, host.ctypes.data_as(C.c_void_p), n, C.c_void_p(ptr), nbytes, st))
+
+    def _validated(self, host: np.ndarray, unique: bool = False) -> np.ndarray:
+        if host.size and (host.min() < 0 or host.max() >= self.num_blocks):
+            raise _lib.EmmError(_lib.ERR_ID_RANGE, f"block id outside [0, {self.num_blocks})")
+        if unique and np.unique(host).size != host.size:
+            raise _lib.EmmError(_lib.ERR_DUPLICATE, "duplicate destination block id")
+        return host
+
+    def copy_blocks(self, dst: "KVPool", src_ids: IdList, dst_ids: IdList) -> None:
+        """dst[l][p, dst_ids[i]] = self[l][p, src_ids[i]] with no staging buffer."""
+        if dst.ctx is not self.ctx:
+            raise ValueError("both pools must belong to the same Context")
+        lib = self.ctx._lib
+        st = C.c_void_p(_stream_ptr(self.device))
+        dev_tables = isinstance(src_ids, torch.Tensor) and src_ids.is_cuda
+        if dev_tables != (isinstance(dst_ids, torch.Tensor) and dst_ids.is_cuda):
+            raise ValueError("src_ids and dst_ids must both be host lists or both device tensors")
+        if dev_tables:
+            self._check_table(src_ids, self.device)
+            self._check_table(dst_ids, self.device)
+            if src_ids.numel() != dst_ids.numel():
+                raise _lib.EmmError(_lib.ERR_LENGTH, "src_ids and dst_ids differ in length")
+            _lib.check(lib.emm_copy_blocks(self._h, dst._h, C.c_void_p(src_ids.data_ptr()),
+                                           C.c_void_p(dst_ids.data_ptr()), src_ids.numel(), st))
+            return
+        hs, hd = _as_host_ids(src_ids), _as_host_ids(dst_ids)
+        if hs.shape != hd.shape:
+            raise _lib.EmmError(_lib.ERR_LENGTH, "src_ids and dst_ids differ in length")
+        _lib.check(lib.emm_copy_blocks_h(self._h, dst._h, hs.ctypes.data_as(C.c_void_p),
+                                         hd.ctypes.data_as(C.c_void_p), hs.shape[0], st))
+
+    # -- per-token append ------------------------------------------------------
+    def _check_kv(self, key: torch.Tensor, value: torch.Tensor, slot_mapping: torch.Tensor,
+                  lead: int) -> int:
+        want_tail = (self.num_kv_heads, self.head_size)
+        for name, t in (("key", key), ("value", value)):
+            if t.dim() != lead + 3 or tuple(t.shape[-2:]) != want_tail:
+                raise ValueError(f"{name} must be [{'L, ' if lead else ''}T, H, D] with H, D = {want_tail}")
+            if t.dtype != self.dtype or t.device != self.device:
+                raise ValueError(f"{name} must have the pool's dtype and device")
+            if t.stride(-1) != 1 or t.stride(-2) != self.head_size:
+                raise ValueError(f"{name} heads must be contiguous ([H, D] dense per token)")
+        if key.shape != value.shape:
+            raise ValueError("key and value shapes differ")
+        T = key.shape[lead]
+        if (slot_mapping.dtype != torch.int64 or slot_mapping.dim() != 1 or slot_mapping.numel() != T
+                or slot_mapping.device != self.device or not slot_mapping.is_contiguous()):
+            raise ValueError("slot_mapping must be a contiguous int64 device tensor with one entry per token")
+        return T
+
+    def append(self, layer: int, key: torch.Tensor, value: torch.Tensor,
+               slot_mapping: torch.Tensor) -> None:
+        """reshape_and_cache for one layer; slot < 0 entries are skipped."""
+        T = self._check_kv(key, value, slot_mapping, 0)
+        e = self.elem_size
+        _lib.check(self.ctx._lib.emm_append(
+            self._h, layer, C.c_void_p(key.data_ptr()), C.c_void_p(value.data_ptr()),
+            key.stride(0) * e, value.stride(0) * e, C.c_void_p(slot_mapping.data_ptr()), T,
+            C.c_void_p(_stream_ptr(self.device))))
+
+    def append_all_layers(self, key: torch.Tensor, value: torch.Tensor,
+                          slot_mapping: torch.Tensor) -> None:
+        """reshape_and_cache for every layer in one launch; key/value are [L, T, H, D]."""
+        T = self._check_kv(key, value, slot_mapping, 1)
+        if key.shape[0] != self.num_layers:
+            raise ValueError(f"key has {key.shape[0]} layers, pool has {self.num_layers}")
+        e = self.elem_size
+        _lib.check(self.ctx._lib.emm_append_all_layers(
+            self._h, C.c_void_p(key.data_ptr()), C.c_void_p(value.data_ptr()),
+            key.stride(0) * e, key.stride(1) * e, value.stride(0) * e, value.stride(1) * e,
+            C.c_void_p(slot_mapping.data_ptr()), T, C.c_void_p(_stream_ptr(self.device))))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h:
+            self.ctx._lib.emm_pool_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def compact_plan(table_ids: Sequence[int], num_blocks: int) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Minimal-move defragmentation plan (host only, emm_compact_plan).
+
+    Returns (new_table_ids, move_src, move_dst). Needs no GPU.
+    """
+    lib = _lib.load()
+    ids = np.ascontiguousarray(table_ids, dtype=np.int64)
+    n = ids.shape[0]
+    new_ids = np.empty(n, dtype=np.int64)
+    src = np.empty(n, dtype=np.int64)
+    dst = np.empty(n, dtype=np.int64)
+    moves = C.c_int64()
+    p = lambda a: a.ctypes.data_as(C.POINTER(C.c_int64))
+    _lib.check(lib.emm_compact_plan(p(ids), n, int(num_blocks), p(new_ids), p(src), p(dst), C.byref(moves)))
+    m = moves.value
+    return new_ids, src[:m].copy(), dst[:m].copy()

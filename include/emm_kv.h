@@ -1,0 +1,247 @@
+/*
+ * emm_kv.h -- C ABI of the paged KV-cache movement library (sm_100a).
+ *
+ * One shared library, plain C types only. Every data entry point takes raw
+ * device pointers, element counts and a CUDA stream (passed as void*, it is a
+ * cudaStream_t). Launches are asynchronous and stream ordered; nothing here
+ * synchronises the device except emm_ctx_status() and the *_create/_destroy
+ * calls. Errors are returned as int status codes (0 = ok), never thrown; the
+ * text of the last failure on the calling thread is kept for
+ * emm_last_error(). This mirrors the reference's convention of returning
+ * {"error": ..., "bytes": 0} from its data path instead of raising
+ * (elasticmm/engine/v0/worker.py:686-691,726-731,860-871).
+ *
+ * The reference has no FFI for this path: its data plane is a set of Python
+ * methods on the V0Worker actor built from torch indexing kernels. Each entry
+ * below names the reference method whose device work it replaces.
+ *
+ * Pool layout. A pool is L per-layer allocations. Inside a layer:
+ *   address(plane p, block b, token t, head h) =
+ *       layer_ptr[l] + p*plane_stride + b*block_stride + t*token_stride + h*head_stride
+ * with head_size*elem_size contiguous bytes at that address. The reference
+ * layout is a list of L tensors [2, NB, BS, H, D]
+ * (elasticmm/engine/v0/worker.py:388-394,593-594): plane_stride = NB*page,
+ * block_stride = page, token_stride = H*D*e, head_stride = D*e, where
+ * page = BS*H*D*e. Whole-block operations need the BS*H*D*e bytes of one
+ * block of one plane to be one dense run ("page"); both the reference order
+ * (token-major) and the head-major order satisfy that.
+ *
+ * Packed transfer buffer: [L, 2, n, page] contiguous, the byte image of the
+ * tensor [L, 2, n, BS, H, D] that extract_kv_blocks returns
+ * (elasticmm/engine/v0/worker.py:578-610).
+ */
+#ifndef EMM_KV_H
+#define EMM_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EMM_KV_ABI_VERSION 1
+
+typedef struct emm_ctx emm_ctx;   /* one per process and device; not thread safe */
+typedef struct emm_pool emm_pool; /* geometry + per-layer base pointers of one pool */
+
+enum emm_status {
+  EMM_OK = 0,
+  EMM_ERR_BAD_ARG = 1,    /* null pointer, negative count, unsupported geometry */
+  EMM_ERR_ID_RANGE = 2,   /* a block id or slot outside the pool */
+  EMM_ERR_LENGTH = 3,     /* buffer size / block count mismatch */
+  EMM_ERR_CUDA = 4,       /* a CUDA runtime call failed; text in emm_last_error */
+  EMM_ERR_TIMEOUT = 5,    /* a bounded device-side wait ran out */
+  EMM_ERR_ALIGN = 6,      /* pointer or stride alignment below element size */
+  EMM_ERR_DUPLICATE = 7,  /* duplicate destination ids (write order undefined) */
+  EMM_ERR_OVERLAP = 8,    /* source and destination id sets overlap in one pool */
+  EMM_ERR_TOO_LARGE = 9,  /* request exceeds a fixed capacity */
+  EMM_ERR_NOMEM = 10      /* host or device allocation failed */
+};
+
+typedef struct emm_pool_desc {
+  int32_t num_layers;   /* L */
+  int32_t num_blocks;   /* NB, blocks per layer and plane */
+  int32_t block_size;   /* BS, tokens per block */
+  int32_t num_kv_heads; /* H */
+  int32_t head_size;    /* D */
+  int32_t elem_size;    /* bytes per element: 2 for fp16/bf16, 1 for fp8, 4 for fp32 */
+  int64_t plane_stride; /* bytes from the K plane to the V plane of a layer */
+  int64_t block_stride; /* bytes between consecutive blocks of a plane */
+  int64_t token_stride; /* bytes between consecutive tokens of a block */
+  int64_t head_stride;  /* bytes between consecutive heads of a token */
+} emm_pool_desc;
+
+/* Copy-kernel families, for emm_ctx_set_option(ctx, EMM_OPT_COPY_VARIANT, v). */
+enum emm_copy_variant {
+  EMM_COPY_AUTO = 0, /* library default */
+  EMM_COPY_BULK = 1, /* cp.async.bulk global->shared->global ring, one issuing lane per warp */
+  EMM_COPY_LDG = 2   /* 16-byte vector loads/stores through registers */
+};
+
+enum emm_option {
+  EMM_OPT_COPY_VARIANT = 0,  /* enum emm_copy_variant */
+  EMM_OPT_CHUNK_BYTES = 1,   /* bytes per work item of the copy kernels (multiple of 16) */
+  EMM_OPT_STAGES = 2,        /* shared-memory ring depth per warp, bulk variant (2..8) */
+  EMM_OPT_WARPS = 3,         /* issuing warps per CTA, bulk variant (1..8) */
+  EMM_OPT_CTAS_PER_SM = 4,   /* resident CTAs per SM the grid is sized for */
+  EMM_OPT_LDG_UNROLL = 5,    /* 16-byte loads in flight per thread, LDG variant (1,2,4,8) */
+  EMM_OPT_MAX_CTAS = 6       /* cap on the grid (0 = none); used by the peer-store path */
+};
+
+/* ---- library ---------------------------------------------------------- */
+
+int emm_abi_version(void);
+const char *emm_status_string(int status);
+/* Text of the most recent failure on this thread ("" if none). */
+const char *emm_last_error(void);
+
+/* ---- context ---------------------------------------------------------- */
+
+/* Binds to `device`, creates the device status word and the id staging ring.
+ * Replaces nothing in the reference (it keeps no native state). */
+int emm_ctx_create(int device, emm_ctx **out);
+int emm_ctx_destroy(emm_ctx *ctx);
+int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value);
+int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value);
+/* Number of kernels this context has launched so far. */
+int64_t emm_ctx_launch_count(emm_ctx *ctx);
+/* Waits for `stream`, then returns and clears the sticky device-side status
+ * (EMM_OK, EMM_ERR_ID_RANGE, EMM_ERR_TIMEOUT). The kernels never trap: a bad
+ * id is recorded here and the page is skipped. `detail` (may be NULL)
+ * receives the offending id or slot. */
+int emm_ctx_status(emm_ctx *ctx, void *stream, int64_t *detail);
+
+/* ---- pools ------------------------------------------------------------ */
+
+/* Fills `desc` with the reference layout [2, NB, BS, H, D] per layer
+ * (elasticmm/engine/v0/worker.py:593-594). */
+int emm_pool_desc_nhd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, int elem_size);
+/* Same geometry with heads before tokens inside a block: [2, NB, H, BS, D]. */
+int emm_pool_desc_hnd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, int elem_size);
+
+/* `layer_ptrs` is a HOST array of L device (or device-visible) base
+ * addresses; the library keeps a device copy. A single 6-D tensor
+ * [L, 2, NB, BS, H, D] (elasticmm/engine/v0/nccl_transfer.py:215,241-244) is
+ * passed as L pointers base + l*layer_bytes. The memory stays owned by the
+ * caller. Also the source of get_kv_cache_layout
+ * (elasticmm/engine/v0/worker.py:635-647). */
+int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *layer_ptrs,
+                    emm_pool **out);
+int emm_pool_destroy(emm_pool *pool);
+int emm_pool_get_desc(const emm_pool *pool, emm_pool_desc *desc);
+/* Bytes of one block of one plane of one layer (BS*H*D*elem_size). */
+int64_t emm_pool_page_bytes(const emm_pool *pool);
+
+/* ---- whole-block movement --------------------------------------------- */
+
+/* Gather: packed[l][p][i] = pool[l][p][ids[i]] for all layers and both
+ * planes, one launch. `d_ids` is a DEVICE int32 array of n block ids.
+ * `packed_bytes` must equal L*2*n*page. Replaces the L index launches plus
+ * torch.stack of V0Worker.extract_kv_blocks
+ * (elasticmm/engine/v0/worker.py:578-610) and the gather half of p2p_send_kv
+ * (:676-678) and of V0NCCLTransferManager.transfer_kv_cache_blocks
+ * (elasticmm/engine/v0/nccl_transfer.py:241-247). */
+int emm_gather(emm_pool *pool, const int32_t *d_ids, int32_t n, void *d_packed,
+               uint64_t packed_bytes, void *stream);
+
+/* Scatter: pool[l][p][ids[i]] = packed[l][p][i]. Duplicate ids give an
+ * undefined winner, as in the reference. Replaces the L index_put launches of
+ * V0Worker.write_kv_blocks (elasticmm/engine/v0/worker.py:612-633), the
+ * scatter half of p2p_recv_kv / p2p_coordinated_transfer_kv (:721,819) and
+ * the per-block loop at elasticmm/engine/v0/nccl_transfer.py:288-289. */
+int emm_scatter(emm_pool *pool, const int32_t *d_ids, int32_t n, const void *d_packed,
+                uint64_t packed_bytes, void *stream);
+
+/* Same two operations on a layer range [layer_begin, layer_begin+layer_count):
+ * the packed pointer addresses that range only ([layer_count, 2, n, page]).
+ * This is the per-layer message of the reference's pipelined send/recv
+ * (elasticmm/engine/v0/worker.py:676-682,804-820). */
+int emm_gather_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
+                      const int32_t *d_ids, int32_t n, void *d_packed, uint64_t packed_bytes,
+                      void *stream);
+int emm_scatter_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
+                       const int32_t *d_ids, int32_t n, const void *d_packed,
+                       uint64_t packed_bytes, void *stream);
+
+/* Block copy: dst[l][p][dst_ids[i]] = src[l][p][src_ids[i]] with no staging
+ * buffer. src and dst may be the same pool (compaction; id sets must not
+ * overlap), two pools on one GPU, a pool in pinned host memory (swap), or a
+ * peer GPU's pool mapped into this process (migration by direct store). Both
+ * pools must have equal page size and layer count. Replaces the per-block
+ * copy loop of V0Worker.swap_blocks (elasticmm/engine/v0/worker.py:520-526)
+ * and extract_kv_blocks followed by write_kv_blocks. */
+int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
+                    const int32_t *d_dst_ids, int32_t n, void *stream);
+
+/* Host-id forms: `h_ids` are HOST int64 arrays (the reference passes Python
+ * lists and uploads them with a synchronous torch.tensor(..., device=...),
+ * elasticmm/engine/v0/worker.py:597,628). The ids are range checked (and,
+ * for destinations, checked for duplicates) on the host, staged through a
+ * pinned ring and uploaded on `stream` without a device synchronisation. */
+int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed,
+                 uint64_t packed_bytes, void *stream);
+int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d_packed,
+                  uint64_t packed_bytes, void *stream);
+int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
+                      const int64_t *h_dst_ids, int32_t n, void *stream);
+
+/* ---- per-token append -------------------------------------------------- */
+
+/* reshape_and_cache for one layer: for each token t with s = slot_mapping[t],
+ * s < 0 is skipped, otherwise K[s / BS][s % BS][:, :] = key[t] and the same
+ * for V. key/value are [T, H, D] with the given token stride in bytes (heads
+ * contiguous: head stride D*elem_size). `d_slot_mapping` is a DEVICE int64
+ * array. In the reference this is vLLM's cache op reached under
+ * model_runner.execute_model (elasticmm/engine/v0/worker_steps.py:281,438);
+ * the slot mapping derives from the reference's block tables (:219,411). */
+int emm_append(emm_pool *pool, int32_t layer, const void *d_key, const void *d_value,
+               int64_t key_token_stride, int64_t value_token_stride,
+               const int64_t *d_slot_mapping, int32_t num_tokens, void *stream);
+
+/* All layers of one decode step in one launch: key/value are [L, T, H, D]
+ * with the given layer and token strides in bytes; one slot mapping is
+ * shared by all layers (every layer of a request uses the same block table,
+ * elasticmm/engine/v0/worker_steps.py:406-420). */
+int emm_append_all_layers(emm_pool *pool, const void *d_key, const void *d_value,
+                          int64_t key_layer_stride, int64_t key_token_stride,
+                          int64_t value_layer_stride, int64_t value_token_stride,
+                          const int64_t *d_slot_mapping, int32_t num_tokens, void *stream);
+
+/* ---- compaction planning (host only) ---------------------------------- */
+
+/* Minimal-move defragmentation plan. `table_ids` holds the concatenated
+ * block tables of the live requests, `n_ids` entries in total, each id in
+ * [0, num_blocks) and unique. After the plan every live block has an id in
+ * [0, n_ids): live blocks whose id is already < n_ids stay; the others move,
+ * in table order, into the free ids < n_ids in ascending order (so source
+ * and destination sets are disjoint). Outputs: `new_table_ids[n_ids]` (the
+ * rewritten tables), `move_src` / `move_dst` (capacity n_ids each) and
+ * `*n_moves`. The reference has no compaction; its free list only ever
+ * appends freed ids (elasticmm/engine/v0/block_manager.py:247-256), which is
+ * what fragments the tables. */
+int emm_compact_plan(const int64_t *table_ids, int64_t n_ids, int64_t num_blocks,
+                     int64_t *new_table_ids, int64_t *move_src, int64_t *move_dst,
+                     int64_t *n_moves);
+
+/* ---- peer mapping (multi-GPU, one process per GPU) --------------------- */
+
+#define EMM_IPC_HANDLE_BYTES 64
+
+/* Exports the allocation containing `d_ptr` for another process on the same
+ * node: `handle` names the allocation, `*offset` is d_ptr's distance from
+ * its base. The reference only sketches this (register_ipc_handle,
+ * elasticmm/engine/v0/kv_transfer.py:89-111; get_ipc_handles returns [],
+ * elasticmm/engine/v0/worker.py:415-437). */
+int emm_ipc_export(emm_ctx *ctx, const void *d_ptr, unsigned char handle[EMM_IPC_HANDLE_BYTES],
+                   uint64_t *offset);
+/* Maps a peer allocation and returns the peer address of the exported
+ * pointer. A handle is opened once per process and cached; emm_ctx_destroy
+ * closes the mappings. */
+int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES], uint64_t offset,
+                 void **d_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMM_KV_H */
