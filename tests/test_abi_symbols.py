@@ -1,0 +1,74 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from elasticmm_b200 import _lib
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(__file__)), "include", "emm_kv.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(emm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.load()
+    names = declared_functions()
+    assert len(names) >= 25
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in emm_kv.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes prototype"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_abi_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.emm_abi_version() == 1
+    assert lib.emm_status_string(_lib.OK) == b"ok"
+    seen = {lib.emm_status_string(c) for c in range(0, 11)}
+    assert len(seen) == 11 and b"unknown status" not in seen
+    assert lib.emm_status_string(99) == b"unknown status"
+
+
+def test_status_codes_match_header():
+    text = open(HEADER).read()
+    for name, value in re.findall(r"(EMM_(?:OK|ERR_[A-Z_]+))\s*=\s*(\d+)", text):
+        py = name[len("EMM_"):]
+        assert getattr(_lib, py) == int(value), name
+
+
+def test_pool_desc_presets_need_no_gpu():
+    lib = _lib.load()
+    d = _lib.PoolDesc()
+    assert lib.emm_pool_desc_nhd(C.byref(d), 32, 2048, 16, 32, 128, 2) == 0
+    page = 16 * 32 * 128 * 2
+    assert (d.block_stride, d.plane_stride, d.token_stride, d.head_stride) == (page, page * 2048, 32 * 256, 256)
+    assert lib.emm_pool_desc_hnd(C.byref(d), 28, 64, 16, 4, 128, 2) == 0
+    assert (d.token_stride, d.head_stride) == (256, 16 * 256)
+    assert lib.emm_pool_desc_nhd(C.byref(d), 0, 1, 1, 1, 1, 2) == _lib.ERR_BAD_ARG
+    assert lib.emm_pool_desc_nhd(C.byref(d), 1, 1, 1, 1, 1, 3) == _lib.ERR_BAD_ARG
+    assert b"elem_size" in lib.emm_last_error()
+
+
+def test_context_creation_fails_loudly_without_a_device():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    lib = _lib.load()
+    h = C.c_void_p()
+    rc = lib.emm_ctx_create(0, C.byref(h))
+    assert rc == _lib.ERR_CUDA and not h.value
+    assert lib.emm_last_error() != b""
+    from elasticmm_b200 import get_context
+    from elasticmm_b200.engine.v0 import V0Worker
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        get_context(0)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        V0Worker()

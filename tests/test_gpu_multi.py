@@ -1,0 +1,149 @@
+"""Prefill -> decode migration between GPUs (one process per GPU, NCCL + peer-mapped pools).
+Skipped on a box with a single GPU."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+GEOM = dict(L=28, NB=512, BS=16, H=4, D=128)   # Qwen2.5-VL-7B-shaped pages on a reduced pool
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _requests(seed):
+    g = torch.Generator().manual_seed(seed)
+    sperm = torch.randperm(GEOM["NB"], generator=g).tolist()
+    dperm = torch.randperm(GEOM["NB"], generator=g).tolist()
+    out, pos = [], 0
+    for i in range(6):
+        tokens = 576 + int(torch.randint(32, 1025, (1,), generator=g))
+        n = -(-tokens // GEOM["BS"])
+        if pos + n > GEOM["NB"]:
+            break
+        out.append((f"r{i}", sperm[pos:pos + n], dperm[pos:pos + n]))
+        pos += n
+    return out
+
+
+def _worker_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer, TransferMethod, V0KVTransferManager, V0Worker
+    from oracle import kv_oracle
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dev = torch.device("cuda", rank)
+
+    def fresh(seed, guard):
+        cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, seed,
+                                  fill="guard" if guard else "normal")
+        w = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
+                     kv_cache=[t.to(dev) for t in cpu])
+        assert w.init_global_nccl()
+        return w, cpu
+
+    def expect(reqs):
+        src_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 70)
+        want = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0,
+                                   fill="guard")
+        for _, s, d in reqs:
+            kv_oracle.write_kv_blocks(want, d, kv_oracle.extract_kv_blocks(src_cpu, s))
+        return want
+
+    def same(w, want):
+        return all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, want))
+
+    results = {}
+    reqs = _requests(3)
+
+    # 1. staged NCCL, request by request, through the manager (source sends, sink receives)
+    w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    mgr = V0KVTransferManager(transfer_method=TransferMethod.NCCL)
+    mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+    oks = [mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs]
+    results["nccl_ok"] = all(oks)
+    if rank == 1:
+        results["nccl_exact"] = same(w, expect(reqs))
+        results["nccl_bytes"] = mgr.last_result["bytes"]
+    dist.barrier()
+
+    # 2. direct peer stores: map the sink's pool into the source, one launch per request
+    w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    handles = [None] * world
+    dist.all_gather_object(handles, (w.get_ipc_handles(), w.get_pool_desc()))
+    for peer in range(world):
+        if peer != rank:
+            w.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
+    mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
+    mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+    oks = [mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs]
+    results["peer_ok"] = all(oks)
+    dist.barrier()
+    if rank == 1:
+        results["peer_exact"] = same(w, expect(reqs))
+    dist.barrier()
+
+    # 3. plan level, both methods, all requests as one table per pair
+    for method in ("peer", "nccl"):
+        w2, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+        if method == "peer":
+            h2 = [None] * world
+            dist.all_gather_object(h2, (w2.get_ipc_handles(), w2.get_pool_desc()))
+            for peer in range(world):
+                if peer != rank:
+                    w2.attach_peer_pool(peer, h2[peer][0], h2[peer][1])
+        plan = MigrationPlan([Transfer(rid, 0, 1, tuple(s), tuple(d)) for rid, s, d in reqs])
+        res = w2.migrate(plan, method=method)
+        results[f"plan_{method}_ok"] = "error" not in res
+        dist.barrier()
+        if rank == 1:
+            results[f"plan_{method}_exact"] = same(w2, expect(reqs))
+        dist.barrier()
+
+    # 4. exchange: both ranks are source and sink at once (peer method only)
+    w3, _ = fresh(70, guard=False)
+    sink_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0,
+                                   fill="guard")
+    sink = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
+                    kv_cache=[t.to(dev) for t in sink_cpu])
+    h3 = [None] * world
+    dist.all_gather_object(h3, (sink.get_ipc_handles(), sink.get_pool_desc()))
+    w3.init_global_nccl()
+    for peer in range(world):
+        if peer != rank:
+            w3.attach_peer_pool(peer, h3[peer][0], h3[peer][1])
+    plan = MigrationPlan([Transfer(f"{rid}-{src}", src, 1 - src, tuple(s), tuple(d))
+                          for src in (0, 1) for rid, s, d in _requests(3 + src)])
+    res = w3.migrate(plan, method="peer")
+    results["exchange_ok"] = "error" not in res
+    dist.barrier()
+    mine = [(rid, s, d) for rid, s, d in _requests(3 + (1 - rank))]
+    results["exchange_exact"] = same(sink, expect(mine))
+    dist.barrier()
+
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_migration_is_bit_exact():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        r0, r1 = torch.load(os.path.join(d, "r0.pt")), torch.load(os.path.join(d, "r1.pt"))
+    for r in (r0, r1):
+        for k, v in r.items():
+            if k.endswith("_ok") or k.endswith("_exact"):
+                assert v, f"{k} failed: {r}"
+    assert r1["nccl_bytes"] > 0
