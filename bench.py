@@ -371,9 +371,10 @@ def bench_single(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
         "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
-                   "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(waves),
+                   "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(waves), "small": args.small,
                    "payload_gib_per_step": round(payload / GIB, 2), "path": "gather -> packed buffer -> scatter",
-                   "l2": "inputs larger than L2 (two 16 GiB pools, 64 MiB..1 GiB per launch)",
+                   "l2": f"inputs larger than L2 (two {w['NB'] * block_bytes(w) / GIB:.0f} GiB pools, "
+                         f"{min(counts) * block_bytes(w) >> 20}..{max(counts) * block_bytes(w) >> 20} MiB per launch)",
                    "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
         "verified_bit_exact_checksum": verified,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -428,9 +429,6 @@ def bench_append(ctx, device, args):
 
     steps = max(args.steps, 50)
     out = {"workload": "append_cfg2", "tokens_per_step": T, "valid_tokens": valid, "layers": L}
-    ms = timed(per_layer, steps, 5, device)
-    out["per_layer_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
-                              "launches_per_step": L}
     ms = timed(all_layers, steps, 5, device)
     row = H * D * 2
     algo = valid * L * (4 * row + 8)  # K and V rows read and written, plus the slot
@@ -438,6 +436,9 @@ def bench_append(ctx, device, args):
     out["all_layers_call"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
                               "launches_per_step": 1, "hbm_gbs": round(algo * steps / (ms / 1e3) / 1e9, 1),
                               "frac_of_peak": round(algo * steps / (ms / 1e3) / 1e9 / peak, 4), "peak_kind": f"of {kind}"}
+    ms = timed(per_layer, steps, 5, device)
+    out["per_layer_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
+                              "launches_per_step": L}
     # CUDA-graph replay of the per-layer sequence (how a captured decode step issues it)
     try:
         stream = torch.cuda.Stream(device)
@@ -678,6 +679,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--small", action="store_true",
+                    help="N=1: the same geometries on pools of a few GiB and 8 requests (the case profiled under ncu)")
     ap.add_argument("--skip-extras", action="store_true", help="N=1: skip the append and compaction objects")
     ap.add_argument("--skip-cpu", action="store_true", help="N=1: skip the CPU baseline leg")
     ap.add_argument("--variant", type=int, default=None, help="copy kernel family (1 bulk, 2 ldg)")
@@ -688,6 +691,10 @@ def main():
     ap.add_argument("--unroll", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.small:
+        WORKLOADS["llama7b_cfg1"].update(NB=256, requests=8)
+        WORKLOADS["append_cfg2"].update(NB=1024)
+        WORKLOADS["gqa70b_cfg5"].update(NB=512, tokens=("uniform", 512, 2048))
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -90,10 +90,10 @@ struct emm_ctx {
   // options
   int copy_variant = EMM_COPY_AUTO;
   int64_t chunk_bytes = 0;  // 0 = per-variant default
-  int stages = 4;
-  int warps = 4;
+  int stages = 2;
+  int warps = 0;            // 0 = sized from the chunk (see launch_page_copy)
   int ctas_per_sm = 0;      // 0 = per-variant default
-  int ldg_unroll = 4;
+  int ldg_unroll = 2;
   int max_ctas = 0;
   int bulk_smem_set = 0;    // dynamic smem limit already applied to the bulk kernel
   IdSlot ring[kRingSlots];
@@ -257,38 +257,51 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   a.status = ctx->d_status;
 
   int64_t chunk = ctx->chunk_bytes;
-  if (chunk <= 0) chunk = (variant == EMM_COPY_BULK) ? 8192 : 256 * 16 * ctx->ldg_unroll;
+  if (chunk <= 0) chunk = (variant == EMM_COPY_BULK) ? 32768 : 65536;
   if (chunk > page_bytes) chunk = page_bytes;
+  int warps = ctx->warps;
+  int auto_ctas_per_sm = 0;
   if (variant == EMM_COPY_BULK) {
+    if (warps <= 0) {
+      // Measured on B200 with a 2-deep ring: throughput peaks sharply at two
+      // lanes per SM for 32 KiB chunks, three for 16 KiB, five for 8 KiB and
+      // eight for 4 KiB (one lane more or fewer costs 5-25 %), that is at
+      // about 32 KiB of loads in flight per SM beyond one chunk.
+      const int64_t in_flight = (int64_t)(ctx->stages - 1) * chunk;
+      int lanes = (int)(1 + (32 * 1024 + in_flight / 2) / in_flight);
+      lanes = std::max(1, std::min(lanes, 16));
+      warps = std::min(lanes, emm::kMaxWarps);
+      auto_ctas_per_sm = (lanes + warps - 1) / warps;
+    }
     // The ring of warps*stages chunks must fit the opt-in shared memory.
     const int64_t budget = (int64_t)ctx->max_smem_optin - 2048;
-    while ((int64_t)ctx->warps * ctx->stages * chunk > budget && chunk > 1024) chunk /= 2;
+    while ((int64_t)warps * ctx->stages * chunk > budget && chunk > 1024) chunk /= 2;
     chunk &= ~(int64_t)15;
-    if (chunk < 16 || (int64_t)ctx->warps * ctx->stages * chunk > budget)
+    if (chunk < 16 || (int64_t)warps * ctx->stages * chunk > budget)
       return fail(EMM_ERR_BAD_ARG, "bulk ring of %d x %d chunks does not fit shared memory",
-                  ctx->warps, ctx->stages);
+                  warps, ctx->stages);
   }
   a.chunk_bytes = (uint32_t)chunk;
   a.chunks_per_page = (uint32_t)((page_bytes + chunk - 1) / chunk);
   a.total_chunks = (uint64_t)layer_count * 2ull * (uint64_t)n * a.chunks_per_page;
 
   if (variant == EMM_COPY_BULK) {
-    const int smem = (int)((int64_t)ctx->warps * ctx->stages * chunk);
+    const int smem = (int)((int64_t)warps * ctx->stages * chunk);
     if (smem > ctx->bulk_smem_set) {
       EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       ctx->bulk_smem_set = smem;
     }
-    int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm
-                                      : std::max(1, (int)((ctx->max_smem_optin - 2048) / (smem + 1024)));
-    per_sm = std::min(per_sm, 2048 / (ctx->warps * 32));
-    uint64_t want = (a.total_chunks + ctx->warps - 1) / ctx->warps;
+    const int fit = std::max(1, (int)((ctx->max_smem_optin - 2048) / (smem + 1024)));
+    int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : (auto_ctas_per_sm > 0 ? auto_ctas_per_sm : fit);
+    per_sm = std::min(std::min(per_sm, fit), 2048 / (warps * 32));
+    uint64_t want = (a.total_chunks + warps - 1) / warps;
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(want, cap);
-    emm::page_copy_bulk<<<grid, ctx->warps * 32, smem, st>>>(a, (uint32_t)ctx->stages);
+    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages);
   } else {
-    const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : 8;
+    const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : 4;
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(a.total_chunks, cap);
@@ -453,8 +466,8 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       ctx->stages = (int)value;
       return EMM_OK;
     case EMM_OPT_WARPS:
-      if (value < 1 || value > emm::kMaxWarps)
-        return fail(EMM_ERR_BAD_ARG, "warps must be in [1, %d]", emm::kMaxWarps);
+      if (value < 0 || value > emm::kMaxWarps)
+        return fail(EMM_ERR_BAD_ARG, "warps must be in [0, %d] (0 = automatic)", emm::kMaxWarps);
       ctx->warps = (int)value;
       return EMM_OK;
     case EMM_OPT_CTAS_PER_SM:

@@ -203,6 +203,8 @@ class KVPool:
         self.head_size = desc.head_size
         self.elem_size = desc.elem_size
         self.page_bytes = int(lib.emm_pool_page_bytes(handle))
+        self._append_sigs: Dict[tuple, int] = {}
+        self._emm_append = lib.emm_append
         # head-major pages: tokens step by D, heads by BS*D
         self.head_major = (desc.num_kv_heads > 1 and desc.block_size > 1
                            and desc.token_stride == desc.head_size * desc.elem_size)
@@ -363,12 +365,20 @@ class KVPool:
     def append(self, layer: int, key: torch.Tensor, value: torch.Tensor,
                slot_mapping: torch.Tensor) -> None:
         """reshape_and_cache for one layer; slot < 0 entries are skipped."""
-        T = self._check_kv(key, value, slot_mapping, 0)
+        # Called once per layer per step: argument checks are cached by signature.
+        sig = (key.shape, key.stride(), key.dtype, key.device, value.shape, value.stride(), value.dtype,
+               value.device, slot_mapping.shape, slot_mapping.stride(), slot_mapping.dtype, slot_mapping.device)
+        T = self._append_sigs.get(sig)
+        if T is None:
+            T = self._check_kv(key, value, slot_mapping, 0)
+            if len(self._append_sigs) < 64:
+                self._append_sigs[sig] = T
         e = self.elem_size
-        _lib.check(self.ctx._lib.emm_append(
-            self._h, layer, C.c_void_p(key.data_ptr()), C.c_void_p(value.data_ptr()),
-            key.stride(0) * e, value.stride(0) * e, C.c_void_p(slot_mapping.data_ptr()), T,
-            C.c_void_p(_stream_ptr(self.device))))
+        rc = self._emm_append(
+            self._h, layer, key.data_ptr(), value.data_ptr(), key.stride(0) * e, value.stride(0) * e,
+            slot_mapping.data_ptr(), T, torch.cuda.current_stream(self.ctx.device).cuda_stream)
+        if rc:
+            _lib.check(rc)
 
     def append_all_layers(self, key: torch.Tensor, value: torch.Tensor,
                           slot_mapping: torch.Tensor) -> None:

@@ -83,7 +83,7 @@ enum emm_option {
   EMM_OPT_COPY_VARIANT = 0,  /* enum emm_copy_variant */
   EMM_OPT_CHUNK_BYTES = 1,   /* bytes per work item of the copy kernels (multiple of 16) */
   EMM_OPT_STAGES = 2,        /* shared-memory ring depth per warp, bulk variant (2..8) */
-  EMM_OPT_WARPS = 3,         /* issuing warps per CTA, bulk variant (1..8) */
+  EMM_OPT_WARPS = 3,         /* issuing warps per CTA, bulk variant (1..8; 0 = sized from the chunk) */
   EMM_OPT_CTAS_PER_SM = 4,   /* resident CTAs per SM the grid is sized for */
   EMM_OPT_LDG_UNROLL = 5,    /* 16-byte loads in flight per thread, LDG variant (1,2,4,8) */
   EMM_OPT_MAX_CTAS = 6       /* cap on the grid (0 = none); used by the peer-store path */

@@ -5,6 +5,7 @@ from elasticmm_b200 import KVPool, _lib, get_context
 from oracle import kv_oracle
 
 VARIANTS = [
+    dict(variant=_lib.COPY_BULK, chunk_bytes=0, stages=2, warps=0),
     dict(variant=_lib.COPY_BULK, chunk_bytes=0, stages=4, warps=4),
     dict(variant=_lib.COPY_BULK, chunk_bytes=4096, stages=2, warps=1),
     dict(variant=_lib.COPY_BULK, chunk_bytes=16384, stages=3, warps=2),
@@ -13,7 +14,7 @@ VARIANTS = [
     dict(variant=_lib.COPY_LDG, chunk_bytes=2048, ldg_unroll=1),
     dict(variant=_lib.COPY_LDG, chunk_bytes=65536, ldg_unroll=8),
 ]
-DEFAULTS = dict(variant=_lib.COPY_AUTO, chunk_bytes=0, stages=4, warps=4, ctas_per_sm=0, ldg_unroll=4, max_ctas=0)
+DEFAULTS = dict(variant=_lib.COPY_AUTO, chunk_bytes=0, stages=2, warps=0, ctas_per_sm=0, ldg_unroll=2, max_ctas=0)
 
 
 def vid(v):
