@@ -378,7 +378,7 @@ def bench_single(args):
                    "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
         "verified_bit_exact_checksum": verified,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": TRAFFIC_NOTE.get("page_copy"),
+                     "frac": round(achieved / peak, 4), "traffic": round(TRAFFIC_RATIO["page_copy"] * 2 * payload / len(reqs)),
                      "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": round(achieved / 8000.0, 4),
                      "kernel": "page_copy_bulk", "algorithmic_bytes_per_launch":
                          round(2 * payload / len(reqs)), "avg_launch_us": round(ms * 1e3 / launches, 2)},
@@ -393,7 +393,10 @@ def bench_single(args):
     print(json.dumps(line))
 
 
-TRAFFIC_NOTE = {"page_copy": None}  # dram bytes per launch from the committed ncu summary, once captured
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for page_copy_bulk, from the ncu capture
+# summarised in profiles/page_copy_bulk_llama7b_small.md (105-block launch of the --small case); traffic grows in
+# proportion to the blocks a launch moves, so the ratio is scaled to this run's mean launch.
+TRAFFIC_RATIO = {"page_copy": (880.883456 + 832.828416) / (2 * 880.80384)}
 
 
 def bench_append(ctx, device, args):

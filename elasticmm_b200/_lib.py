@@ -38,6 +38,7 @@ OPT_WARPS = 3
 OPT_CTAS_PER_SM = 4
 OPT_LDG_UNROLL = 5
 OPT_MAX_CTAS = 6
+OPT_REMOTE_VARIANT = 7
 
 
 class PoolDesc(C.Structure):

@@ -95,6 +95,7 @@ struct emm_ctx {
   int ctas_per_sm = 0;      // 0 = per-variant default
   int ldg_unroll = 2;
   int max_ctas = 0;
+  int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
   int bulk_smem_set = 0;    // dynamic smem limit already applied to the bulk kernel
   IdSlot ring[kRingSlots];
   int next_slot = 0;
@@ -245,7 +246,8 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
 
   int variant = ctx->copy_variant;
   if (variant == EMM_COPY_AUTO) variant = EMM_COPY_BULK;
-  if (align < 16 || !local) variant = EMM_COPY_LDG;
+  if (!local) variant = ctx->remote_variant;
+  if (align < 16) variant = EMM_COPY_LDG;
 
   PageCopyArgs a;
   a.src = src;
@@ -483,6 +485,11 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       if (value < 0 || value > (1 << 20)) return fail(EMM_ERR_BAD_ARG, "max CTAs out of range");
       ctx->max_ctas = (int)value;
       return EMM_OK;
+    case EMM_OPT_REMOTE_VARIANT:
+      if (value != EMM_COPY_BULK && value != EMM_COPY_LDG)
+        return fail(EMM_ERR_BAD_ARG, "remote variant must be EMM_COPY_BULK or EMM_COPY_LDG");
+      ctx->remote_variant = (int)value;
+      return EMM_OK;
     default:
       return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
@@ -498,6 +505,7 @@ int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
     case EMM_OPT_CTAS_PER_SM: *value = ctx->ctas_per_sm; return EMM_OK;
     case EMM_OPT_LDG_UNROLL: *value = ctx->ldg_unroll; return EMM_OK;
     case EMM_OPT_MAX_CTAS: *value = ctx->max_ctas; return EMM_OK;
+    case EMM_OPT_REMOTE_VARIANT: *value = ctx->remote_variant; return EMM_OK;
     default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
 }

@@ -86,7 +86,8 @@ enum emm_option {
   EMM_OPT_WARPS = 3,         /* issuing warps per CTA, bulk variant (1..8; 0 = sized from the chunk) */
   EMM_OPT_CTAS_PER_SM = 4,   /* resident CTAs per SM the grid is sized for */
   EMM_OPT_LDG_UNROLL = 5,    /* 16-byte loads in flight per thread, LDG variant (1,2,4,8) */
-  EMM_OPT_MAX_CTAS = 6       /* cap on the grid (0 = none); used by the peer-store path */
+  EMM_OPT_MAX_CTAS = 6,      /* cap on the grid (0 = none) */
+  EMM_OPT_REMOTE_VARIANT = 7 /* family used when a side is a peer GPU's or pinned host memory (default LDG) */
 };
 
 /* ---- library ---------------------------------------------------------- */
