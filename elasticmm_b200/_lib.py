@@ -13,6 +13,8 @@ from typing import Optional
 LIB_PATH = Path(__file__).resolve().parent / "libemm_kv.so"
 
 IPC_HANDLE_BYTES = 64
+NOALLOC_MAX_IDS = 16384
+NOALLOC_MAX_LAYERS = 256
 
 # enum emm_status
 OK = 0
@@ -97,6 +99,7 @@ SIGNATURES = {
     "emm_gather_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_scatter_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_copy_blocks_h": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P]),
+    "emm_gather_noalloc": (C.c_int, [C.c_int, C.POINTER(PoolDesc), C.POINTER(_P), _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_append": (C.c_int, [_P, C.c_int32, _P, _P, C.c_int64, C.c_int64, _P, C.c_int32, _P]),
     "emm_append_all_layers": (
         C.c_int,

@@ -919,4 +919,152 @@ int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES],
   return EMM_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Gather without any allocation (see emm_gather_noalloc in emm_kv.h)
+// ---------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+// Fixed scratch inside the library image: [0,16) status word, then the layer
+// pointer array, then the id table. Every GPU that loads the library holds it.
+constexpr size_t kNaStatusBytes = 256;
+constexpr size_t kNaLayersBytes = EMM_NOALLOC_MAX_LAYERS * sizeof(uint64_t);
+constexpr size_t kNaIdsBytes = EMM_NOALLOC_MAX_IDS * sizeof(int32_t);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaStatusBytes + kNaLayersBytes + kNaIdsBytes];
+
+constexpr int kNaMaxDevices = 64;
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on this device
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int smem_set = 0;
+};
+NoAllocDevice g_noalloc_dev[kNaMaxDevices];
+
+// Once per device, with that device current. In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
+int noalloc_setup(int device, NoAllocDevice **out) {
+  if (device < 0 || device >= kNaMaxDevices)
+    return fail(EMM_ERR_BAD_ARG, "gather_noalloc: device %d outside [0, %d)", device, kNaMaxDevices);
+  NoAllocDevice &d = g_noalloc_dev[device];
+  if (!d.ready) {
+    void *ptr = nullptr;
+    EMM_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    EMM_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    EMM_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    d.scratch = static_cast<unsigned char *>(ptr);
+    d.ready = true;
+  }
+  *out = &d;
+  return EMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const *h_layer_ptrs,
+                       const int64_t *h_ids, int32_t n, void *d_packed, uint64_t packed_bytes,
+                       void *stream) {
+  if (!desc || !h_layer_ptrs) return fail(EMM_ERR_BAD_ARG, "gather_noalloc: null descriptor or layer array");
+  bool dense = false;
+  if (int rc = check_desc(*desc, &dense)) return rc;
+  if (!dense) return fail(EMM_ERR_BAD_ARG, "gather_noalloc: pool pages are not dense");
+  if (desc->num_layers > EMM_NOALLOC_MAX_LAYERS)
+    return fail(EMM_ERR_TOO_LARGE, "gather_noalloc: %d layers exceed the fixed maximum of %d",
+                desc->num_layers, EMM_NOALLOC_MAX_LAYERS);
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "gather_noalloc: negative block count");
+  if (n > EMM_NOALLOC_MAX_IDS)
+    return fail(EMM_ERR_TOO_LARGE, "gather_noalloc: %d block ids exceed the fixed maximum of %d", n,
+                EMM_NOALLOC_MAX_IDS);
+  const int64_t page = (int64_t)desc->block_size * desc->num_kv_heads * desc->head_size * desc->elem_size;
+  const uint64_t want = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * (uint64_t)page;
+  if (packed_bytes != want)
+    return fail(EMM_ERR_LENGTH, "gather_noalloc: packed buffer holds %llu bytes, %d blocks need %llu",
+                (unsigned long long)packed_bytes, n, (unsigned long long)want);
+  if (n == 0) return EMM_OK;
+  if (!h_ids || !d_packed) return fail(EMM_ERR_BAD_ARG, "gather_noalloc: null pointer");
+  if (int rc = check_ids_host(h_ids, n, desc->num_blocks, "gather_noalloc")) return rc;
+
+  DeviceGuard guard(device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", device);
+  NoAllocDevice *nd = nullptr;
+  if (int rc = noalloc_setup(device, &nd)) return rc;
+
+  uint32_t align = std::min(pow2_align((uint64_t)desc->plane_stride), pow2_align((uint64_t)desc->block_stride));
+  align = std::min(align, std::min(pow2_align((uint64_t)page), pow2_align((uint64_t)d_packed)));
+  uint64_t layer_addr[EMM_NOALLOC_MAX_LAYERS];
+  for (int l = 0; l < desc->num_layers; ++l) {
+    if (!h_layer_ptrs[l]) return fail(EMM_ERR_BAD_ARG, "gather_noalloc: layer %d base pointer is null", l);
+    layer_addr[l] = (uint64_t)h_layer_ptrs[l];
+    align = std::min(align, pow2_align(layer_addr[l]));
+  }
+  if (align < (uint32_t)desc->elem_size) return fail(EMM_ERR_ALIGN, "gather_noalloc: pointers not aligned to elem_size");
+  int32_t ids32[EMM_NOALLOC_MAX_IDS];
+  for (int32_t i = 0; i < n; ++i) ids32[i] = (int32_t)h_ids[i];
+
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned char *d_status = nd->scratch;
+  unsigned char *d_layers = nd->scratch + kNaStatusBytes;
+  unsigned char *d_ids = d_layers + kNaLayersBytes;
+  // The array keeps the previous call's contents: the status word must start
+  // at zero; the layer array and the table are overwritten up to what is read.
+  EMM_CUDA(cudaMemsetAsync(d_status, 0, 16, st));
+  // Pageable sources: the runtime has copied them out before these calls return.
+  EMM_CUDA(cudaMemcpyAsync(d_layers, layer_addr, sizeof(uint64_t) * desc->num_layers, cudaMemcpyHostToDevice, st));
+  EMM_CUDA(cudaMemcpyAsync(d_ids, ids32, sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
+
+  PageCopyArgs a;
+  a.src.layers = reinterpret_cast<const uint64_t *>(d_layers);
+  a.src.base = 0;
+  a.src.layer_stride = 0;
+  a.src.plane_stride = (uint64_t)desc->plane_stride;
+  a.src.block_stride = (uint64_t)desc->block_stride;
+  a.src.ids = reinterpret_cast<const int32_t *>(d_ids);
+  a.src.num_blocks = (uint32_t)desc->num_blocks;
+  a.dst = packed_side(d_packed, n, page);
+  a.n = (uint32_t)n;
+  a.layer_begin = 0;
+  a.layer_count = (uint32_t)desc->num_layers;
+  a.page_bytes = (uint32_t)page;
+  a.status = reinterpret_cast<int *>(d_status);
+
+  if (align >= 16) {
+    int64_t chunk = std::min<int64_t>(32768, page);
+    const int stages = 2;
+    int lanes = (int)(1 + (32 * 1024 + chunk / 2) / chunk);
+    lanes = std::max(1, std::min(lanes, 16));
+    const int warps = std::min(lanes, emm::kMaxWarps);
+    const int per_sm = (lanes + warps - 1) / warps;
+    a.chunk_bytes = (uint32_t)chunk;
+    a.chunks_per_page = (uint32_t)((page + chunk - 1) / chunk);
+    a.total_chunks = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * a.chunks_per_page;
+    const int smem = (int)(warps * stages * chunk);
+    if (smem > nd->max_smem_optin - 2048)
+      return fail(EMM_ERR_BAD_ARG, "gather_noalloc: ring does not fit shared memory");
+    if (smem > nd->smem_set) {
+      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      nd->smem_set = smem;
+    }
+    const uint64_t want_ctas = (a.total_chunks + warps - 1) / warps;
+    const int grid = (int)std::min<uint64_t>(want_ctas, (uint64_t)nd->sm_count * per_sm);
+    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages);
+  } else {
+    int64_t chunk = std::min<int64_t>(65536, page);
+    a.chunk_bytes = (uint32_t)chunk;
+    a.chunks_per_page = (uint32_t)((page + chunk - 1) / chunk);
+    a.total_chunks = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * a.chunks_per_page;
+    const int grid = (int)std::min<uint64_t>(a.total_chunks, (uint64_t)nd->sm_count * 4);
+    if (align >= 8) emm::page_copy_ldg<uint2, 2><<<grid, 256, 0, st>>>(a);
+    else if (align >= 4) emm::page_copy_ldg<uint32_t, 2><<<grid, 256, 0, st>>>(a);
+    else if (align >= 2) emm::page_copy_ldg<uint16_t, 2><<<grid, 256, 0, st>>>(a);
+    else emm::page_copy_ldg<uint8_t, 2><<<grid, 256, 0, st>>>(a);
+  }
+  EMM_CUDA(cudaGetLastError());
+  return EMM_OK;
+}
+
 }  // extern "C"

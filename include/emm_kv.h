@@ -187,6 +187,30 @@ int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d
 int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
                       const int64_t *h_dst_ids, int32_t n, void *stream);
 
+/* Gather for callers that must not allocate device memory. No counterpart in
+ * the reference. Some hosts cannot afford a cudaMalloc on this path: a serving
+ * process that has already handed nearly all HBM to its own caching allocator
+ * (a raw allocation may fail or fragment it), or a latency-critical section
+ * where the implicit device synchronisation of cudaMalloc / cudaFree is not
+ * acceptable. This entry needs no emm_ctx and no emm_pool (both allocate): the
+ * pool is described by `desc` plus a HOST array of `desc->num_layers` layer
+ * base addresses, the ids are a HOST int64 list, and the device copies of both
+ * live in a fixed array inside the library image (about 66 KiB of device
+ * memory on every GPU that loads the library, held until the process exits).
+ * Limits: n <= EMM_NOALLOC_MAX_IDS, num_layers <= EMM_NOALLOC_MAX_LAYERS;
+ * larger requests return EMM_ERR_TOO_LARGE. Ids are range checked on the host.
+ * The result equals emm_gather_h. The first call on a device looks up the
+ * array's device address and the device's limits; make that first call before
+ * any stream capture begins. All calls share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams, no ordering) race on it;
+ * calls on one stream are safe. Nothing in this call invokes cudaMalloc,
+ * cudaFree or any allocating library routine. */
+#define EMM_NOALLOC_MAX_IDS 16384
+#define EMM_NOALLOC_MAX_LAYERS 256
+int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const *h_layer_ptrs,
+                       const int64_t *h_ids, int32_t n, void *d_packed, uint64_t packed_bytes,
+                       void *stream);
+
 /* ---- per-token append -------------------------------------------------- */
 
 /* reshape_and_cache for one layer: for each token t with s = slot_mapping[t],

@@ -1,0 +1,72 @@
+"""The allocation-free gather entry point against the ordinary one.
+
+Some callers of this library cannot allocate device memory on the KV path: a
+serving process whose own caching allocator already owns almost all of HBM, or
+a section that cannot tolerate the device-wide synchronisation a cudaMalloc or
+cudaFree implies. `emm_gather_noalloc` serves them from a fixed scratch array
+inside the library. This file is collected last on purpose, so a run that
+stops at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from elasticmm_b200 import KVPool, _lib, get_context
+from oracle import kv_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _noalloc_gather(pool: KVPool, ids, out: torch.Tensor) -> int:
+    lib = _lib.load()
+    host = np.ascontiguousarray(ids, dtype=np.int64)
+    ptrs = (C.c_void_p * pool.num_layers)(*pool.layer_ptrs)
+    stream = torch.cuda.current_stream(pool.device).cuda_stream
+    return lib.emm_gather_noalloc(pool.device.index, C.byref(pool.desc), ptrs, host.ctypes.data_as(C.c_void_p),
+                                  len(host), C.c_void_p(out.data_ptr()), out.numel() * out.element_size(),
+                                  C.c_void_p(stream))
+
+
+@pytest.mark.parametrize("geom", [
+    dict(L=4, NB=96, BS=16, H=8, D=128, dtype=torch.bfloat16),   # 32 KiB pages: bulk-copy kernel
+    dict(L=3, NB=40, BS=4, H=3, D=5, dtype=torch.float16),       # 120-byte pages: register kernel
+], ids=["pages_32KiB", "pages_120B"])
+def test_two_calls_in_a_row_match_the_allocating_entry(geom):
+    ctx = get_context(0)
+    cpu = kv_oracle.make_pool(geom["L"], geom["NB"], geom["BS"], geom["H"], geom["D"], geom["dtype"], 17)
+    pool = KVPool([t.cuda() for t in cpu], ctx)
+    g = torch.Generator().manual_seed(3)
+    first = torch.randperm(geom["NB"], generator=g)[:29].tolist()
+    second = torch.randperm(geom["NB"], generator=g)[:11].tolist()   # shorter: stale table entries must not matter
+    for ids in (first, second):
+        want = pool.gather(ids)                       # emm_gather_h
+        got = torch.full_like(want, 7.0)
+        assert _noalloc_gather(pool, ids, got) == _lib.OK, _lib.last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))    # bit-exact, as every parity test here
+        assert kv_oracle.bit_equal(got.cpu(), kv_oracle.extract_kv_blocks(cpu, ids))
+    assert ctx.status()[0] == _lib.OK
+
+
+def test_limits_and_bad_arguments_are_refused_with_a_message():
+    ctx = get_context(0)
+    cpu = kv_oracle.make_pool(2, 8, 4, 2, 8, torch.float16, 1)
+    pool = KVPool([t.cuda() for t in cpu], ctx)
+    out = pool.new_packed(3)
+    lib = _lib.load()
+    too_many = list(range(8)) * ((_lib.NOALLOC_MAX_IDS // 8) + 1)
+    big = torch.empty(1, dtype=torch.float16, device="cuda")
+    assert _noalloc_gather(pool, too_many, big) == _lib.ERR_TOO_LARGE
+    assert b"exceed the fixed maximum" in lib.emm_last_error()
+    assert _noalloc_gather(pool, [0, 1, 8], out) == _lib.ERR_ID_RANGE
+    assert _noalloc_gather(pool, [0, 1], out) == _lib.ERR_LENGTH
+    assert _noalloc_gather(pool, [], pool.new_packed(0)) == _lib.OK
+    layers = _lib.PoolDesc.from_buffer_copy(pool.desc)
+    layers.num_layers = _lib.NOALLOC_MAX_LAYERS + 1
+    ptrs = (C.c_void_p * (layers.num_layers))(*([pool.layer_ptrs[0]] * layers.num_layers))
+    host = np.array([0], dtype=np.int64)
+    rc = lib.emm_gather_noalloc(0, C.byref(layers), ptrs, host.ctypes.data_as(C.c_void_p), 1,
+                                C.c_void_p(out.data_ptr()), 0, None)
+    assert rc == _lib.ERR_TOO_LARGE
