@@ -534,6 +534,9 @@ def bench_multi(args):
     if is_src:
         for peer in sinks:
             worker.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
+    nxt = (rank + 1) % world  # ring neighbour, for the all-ranks exchange variant
+    if nxt not in worker.peer_pools:
+        worker.attach_peer_pool(nxt, handles[nxt][0], handles[nxt][1])
 
     # Requests are split evenly over the sources; each gets a seeded sink. A wave is bounded by the
     # source pool (blocks live at once) and by each sink's pool; source and sink tables are seeded
@@ -543,32 +546,40 @@ def bench_multi(args):
     assign = torch.randint(0, len(sinks), (len(counts),), generator=g).tolist()
     per_src = {s: [i for i in range(len(counts)) if i % len(sources) == k] for k, s in enumerate(sources)}
 
-    def build_plans(n_waves):
+    def build_plans():
+        """Greedy waves: in each wave every source takes its next requests, in order, while they fit its
+        own pool and the pool of the sink they are assigned to."""
         out = []
-        for wv in range(n_waves):
+        cursor = {s: 0 for s in sources}
+        wv = 0
+        while any(cursor[s] < len(per_src[s]) for s in sources):
             plan = MigrationPlan()
             sink_used = {d: 0 for d in sinks}
             sink_perm = {d: torch.randperm(w["NB"], generator=torch.Generator().manual_seed(77 * wv + d)).tolist()
                          for d in sinks}
+            # sinks are shared: give each source an equal share of every sink per wave
+            share = w["NB"] // len(sources)
             for s in sources:
                 perm = torch.randperm(w["NB"], generator=torch.Generator().manual_seed(1000 * wv + s)).tolist()
                 pos = 0
-                for i in per_src[s][wv::n_waves]:
+                used_here = {d: 0 for d in sinks}
+                while cursor[s] < len(per_src[s]):
+                    i = per_src[s][cursor[s]]
                     d, n = sinks[assign[i]], counts[i]
-                    if pos + n > w["NB"] or sink_used[d] + n > w["NB"]:
-                        return None
+                    if pos + n > w["NB"] or used_here[d] + n > max(share, n) or sink_used[d] + n > w["NB"]:
+                        break
                     plan.add(Transfer(f"req{i}", s, d, tuple(perm[pos:pos + n]),
                                       tuple(sink_perm[d][sink_used[d]:sink_used[d] + n])))
                     pos += n
                     sink_used[d] += n
+                    used_here[d] += n
+                    cursor[s] += 1
+            assert plan.transfers, "a request does not fit an empty wave"
             out.append(plan)
+            wv += 1
         return out
 
-    n_waves = max(1, max(len(make_waves([counts[i] for i in per_src[s]], w["NB"])) for s in sources))
-    plans = build_plans(n_waves)
-    while plans is None:
-        n_waves += 1
-        plans = build_plans(n_waves)
+    plans = build_plans()
     total_blocks = sum(p.total_blocks() for p in plans)
     payload = total_blocks * block_bytes(w)
 
@@ -585,10 +596,17 @@ def bench_multi(args):
     def barrier():
         dist.barrier()
 
+    streams = {d: torch.cuda.Stream(device) for d in sinks}
+
     def step_peer():
+        main = torch.cuda.current_stream(device)
         for per in tables:
-            for d, si, di in per:
-                worker.pool.copy_blocks(worker.peer_pools[d], si, di)
+            for d, si, di in per:  # one stream per sink: link-bound pushes run side by side
+                streams[d].wait_stream(main)
+                with torch.cuda.stream(streams[d]):
+                    worker.pool.copy_blocks(worker.peer_pools[d], si, di)
+            for d, _, _ in per:
+                main.wait_stream(streams[d])
             torch.cuda.synchronize(device)
             dist.barrier()  # wave boundary: the sinks may reuse their blocks only after every push landed
 
@@ -636,6 +654,27 @@ def bench_multi(args):
     except Exception as e:
         variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
 
+    # Every rank a source and a sink at once (the rebalancing exchange): rank r stores the lower half of
+    # its pool into the upper half of rank r+1's pool. Run last among the device-resident variants because
+    # it overwrites pool contents.
+    half = w["NB"] // 2
+    ring_src = worker.pool.upload_ids(torch.randperm(half, generator=torch.Generator().manual_seed(rank)).tolist())
+    ring_dst = worker.pool.upload_ids((torch.randperm(half, generator=torch.Generator().manual_seed(50 + rank)) + half).tolist())
+
+    def step_ring():
+        worker.pool.copy_blocks(worker.peer_pools[nxt], ring_src, ring_dst)
+        torch.cuda.synchronize(device)
+        dist.barrier()
+
+    ring_steps = max(3, args.steps // 2)
+    ms_r = max_ms(timed(step_ring, ring_steps, 2, device, barrier))
+    ring_bytes = world * half * block_bytes(w)
+    variants["ring_exchange_all_ranks"] = {
+        "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
+        "per_gpu_egress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
+        "ms_per_step": round(ms_r / ring_steps, 3),
+        "path": "every rank stores half of its pool into the next rank's pool at the same time"}
+
     # end to end through the worker API with host id lists (tables uploaded inside the timed region)
     def step_e2e():
         for plan in plans:
@@ -655,8 +694,8 @@ def bench_multi(args):
             "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
                        "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(plans),
                        "payload_gib_per_step": round(payload / GIB, 2), "sources": sources, "sinks": sinks,
-                       "path": "one direct-store kernel per (source, sink): local loads, NVLink stores into the "
-                               "sink's peer-mapped pool", "l2": "inputs larger than L2",
+                       "path": "one direct-store kernel per (source, sink), sinks served concurrently on separate "
+                               "streams: local loads, NVLink stores into the sink's peer-mapped pool", "l2": "inputs larger than L2",
                        "per_source_egress_gbs": round(per_src_gbs, 2),
                        "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
             "verified_bit_exact_checksum": verified,

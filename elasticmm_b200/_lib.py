@@ -57,6 +57,8 @@ class PoolDesc(C.Structure):
         ("block_stride", C.c_int64),
         ("token_stride", C.c_int64),
         ("head_stride", C.c_int64),
+        ("num_planes", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -87,6 +89,7 @@ SIGNATURES = {
     "emm_ctx_status": (C.c_int, [_P, _P, _I64P]),
     "emm_pool_desc_nhd": (C.c_int, [C.POINTER(PoolDesc)] + [C.c_int] * 6),
     "emm_pool_desc_hnd": (C.c_int, [C.POINTER(PoolDesc)] + [C.c_int] * 6),
+    "emm_pool_desc_blocks": (C.c_int, [C.POINTER(PoolDesc)] + [C.c_int] * 5),
     "emm_pool_create": (C.c_int, [_P, C.POINTER(PoolDesc), C.POINTER(_P), C.POINTER(_P)]),
     "emm_pool_destroy": (C.c_int, [_P]),
     "emm_pool_get_desc": (C.c_int, [_P, C.POINTER(PoolDesc)]),

@@ -109,6 +109,7 @@ struct emm_pool {
   uint64_t *d_layers = nullptr;
   std::vector<uint64_t> h_layers;
   int64_t page_bytes = 0;
+  int planes = 2;
   uint32_t align = 1;   // power-of-two alignment shared by all page addresses
   bool device_local = true;  // every layer pointer is plain memory of ctx->device
 };
@@ -127,11 +128,14 @@ int check_desc(const emm_pool_desc &d, bool *dense_page) {
                 d.num_layers, d.num_blocks, d.block_size, d.num_kv_heads, d.head_size);
   if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4 && d.elem_size != 8)
     return fail(EMM_ERR_BAD_ARG, "elem_size %d not in {1,2,4,8}", d.elem_size);
+  if (d.num_planes < 0 || d.num_planes > 2 || d.reserved != 0)
+    return fail(EMM_ERR_BAD_ARG, "num_planes must be 0, 1 or 2 and reserved must be 0");
   const int64_t e = d.elem_size;
   const int64_t head_bytes = (int64_t)d.head_size * e;
   const int64_t page = (int64_t)d.block_size * d.num_kv_heads * head_bytes;
   if (page > (int64_t)0x7fffffff) return fail(EMM_ERR_TOO_LARGE, "page of %lld bytes", (long long)page);
-  if (d.plane_stride < page || d.block_stride < page || d.token_stride < head_bytes ||
+  const bool two_planes = d.num_planes != 1;
+  if ((two_planes && d.plane_stride < page) || d.block_stride < page || d.token_stride < head_bytes ||
       d.head_stride < head_bytes)
     return fail(EMM_ERR_BAD_ARG, "strides smaller than the data they step over");
   if (d.plane_stride % e || d.block_stride % e || d.token_stride % e || d.head_stride % e)
@@ -211,11 +215,11 @@ CopySide pool_side(const emm_pool *p, const int32_t *ids) {
 }
 
 // One side backed by the packed buffer [layers, 2, n, page].
-CopySide packed_side(const void *packed, int32_t n, int64_t page) {
+CopySide packed_side(const void *packed, int32_t n, int64_t page, int planes = 2) {
   CopySide s;
   s.layers = nullptr;
   s.base = (uint64_t)packed;
-  s.layer_stride = 2ull * (uint64_t)n * (uint64_t)page;
+  s.layer_stride = (uint64_t)planes * (uint64_t)n * (uint64_t)page;
   s.plane_stride = (uint64_t)n * (uint64_t)page;
   s.block_stride = (uint64_t)page;
   s.ids = nullptr;
@@ -239,7 +243,7 @@ int launch_ldg_typed(emm_ctx *ctx, const PageCopyArgs &a, int grid, cudaStream_t
 // both sides are ordinary memory of this GPU.
 int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_t layer_begin,
                      int32_t layer_count, int64_t page_bytes, uint32_t align, bool local,
-                     cudaStream_t st) {
+                     cudaStream_t st, int planes = 2) {
   if (n == 0 || layer_count == 0) return EMM_OK;
   DeviceGuard guard(ctx->device);
   if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
@@ -253,6 +257,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   a.src = src;
   a.dst = dst;
   a.n = (uint32_t)n;
+  a.plane_shift = planes == 2 ? 1u : 0u;
   a.layer_begin = (uint32_t)layer_begin;
   a.layer_count = (uint32_t)layer_count;
   a.page_bytes = (uint32_t)page_bytes;
@@ -285,7 +290,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   }
   a.chunk_bytes = (uint32_t)chunk;
   a.chunks_per_page = (uint32_t)((page_bytes + chunk - 1) / chunk);
-  a.total_chunks = (uint64_t)layer_count * 2ull * (uint64_t)n * a.chunks_per_page;
+  a.total_chunks = (uint64_t)layer_count * (uint64_t)planes * (uint64_t)n * a.chunks_per_page;
 
   if (variant == EMM_COPY_BULK) {
     const int smem = (int)((int64_t)warps * ctx->stages * chunk);
@@ -303,7 +308,10 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     const int grid = (int)std::min<uint64_t>(want, cap);
     emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages);
   } else {
-    const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : 4;
+    // A peer or host destination is bound by the link, not by HBM: one CTA per SM
+    // already saturates NVLink (measured), and small grids let pushes to several
+    // sinks run side by side on different streams.
+    const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : (local ? 4 : 1);
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(a.total_chunks, cap);
@@ -339,7 +347,7 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
   if (int rc = check_pool_for_pages(pool, what)) return rc;
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
   if (n < 0) return fail(EMM_ERR_BAD_ARG, "%s: negative block count %d", what, n);
-  const uint64_t want = (uint64_t)layer_count * 2ull * (uint64_t)n * (uint64_t)pool->page_bytes;
+  const uint64_t want = (uint64_t)layer_count * (uint64_t)pool->planes * (uint64_t)n * (uint64_t)pool->page_bytes;
   if (packed_bytes != want)
     return fail(EMM_ERR_LENGTH, "%s: packed buffer holds %llu bytes, %d blocks need %llu", what,
                 (unsigned long long)packed_bytes, n, (unsigned long long)want);
@@ -349,13 +357,13 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
   if (align < (uint32_t)pool->desc.elem_size)
     return fail(EMM_ERR_ALIGN, "%s: packed buffer not aligned to elem_size", what);
   CopySide ps = pool_side(pool, d_ids);
-  CopySide bs = packed_side(d_packed, n, pool->page_bytes);
+  CopySide bs = packed_side(d_packed, n, pool->page_bytes, pool->planes);
   return to_packed ? launch_page_copy(pool->ctx, ps, bs, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream)
+                                      (cudaStream_t)stream, pool->planes)
                    : launch_page_copy(pool->ctx, bs, ps, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream);
+                                      (cudaStream_t)stream, pool->planes);
 }
 
 // Uploads host ids (already validated) into a ring slot; returns the device
@@ -536,6 +544,8 @@ static int fill_desc(emm_pool_desc *d, int L, int NB, int BS, int H, int D, int 
   d->num_kv_heads = H;
   d->head_size = D;
   d->elem_size = e;
+  d->num_planes = 2;
+  d->reserved = 0;
   const int64_t head_bytes = (int64_t)D * e;
   const int64_t page = (int64_t)BS * H * head_bytes;
   d->block_stride = page;
@@ -559,6 +569,25 @@ int emm_pool_desc_hnd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, 
   return fill_desc(desc, L, NB, BS, H, D, elem_size, true);
 }
 
+int emm_pool_desc_blocks(emm_pool_desc *desc, int L, int NB, int rows, int cols, int elem_size) {
+  if (!desc) return fail(EMM_ERR_BAD_ARG, "null descriptor");
+  desc->num_layers = L;
+  desc->num_blocks = NB;
+  desc->block_size = rows;
+  desc->num_kv_heads = 1;
+  desc->head_size = cols;
+  desc->elem_size = elem_size;
+  desc->num_planes = 1;
+  desc->reserved = 0;
+  const int64_t row_bytes = (int64_t)cols * elem_size;
+  desc->token_stride = row_bytes;
+  desc->head_stride = row_bytes;
+  desc->block_stride = row_bytes * rows;
+  desc->plane_stride = 0;
+  bool dense;
+  return check_desc(*desc, &dense);
+}
+
 int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *layer_ptrs,
                     emm_pool **out) {
   if (!ctx || !desc || !layer_ptrs || !out) return fail(EMM_ERR_BAD_ARG, "emm_pool_create: null argument");
@@ -572,8 +601,11 @@ int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *
   if (!p) return fail(EMM_ERR_NOMEM, "emm_pool_create: host allocation failed");
   p->ctx = ctx;
   p->desc = *desc;
+  p->planes = desc->num_planes == 1 ? 1 : 2;
+  p->desc.num_planes = p->planes;
   p->page_bytes = dense ? (int64_t)desc->block_size * desc->num_kv_heads * desc->head_size * desc->elem_size : 0;
-  uint32_t align = std::min(pow2_align((uint64_t)desc->plane_stride), pow2_align((uint64_t)desc->block_stride));
+  uint32_t align = pow2_align((uint64_t)desc->block_stride);
+  if (p->planes == 2) align = std::min(align, pow2_align((uint64_t)desc->plane_stride));
   if (dense) align = std::min(align, pow2_align((uint64_t)p->page_bytes));
   p->h_layers.resize(desc->num_layers);
   for (int l = 0; l < desc->num_layers; ++l) {
@@ -657,8 +689,9 @@ int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
   if (int rc = check_pool_for_pages(src, "copy_blocks(src)")) return rc;
   if (int rc = check_pool_for_pages(dst, "copy_blocks(dst)")) return rc;
   if (src->ctx != dst->ctx) return fail(EMM_ERR_BAD_ARG, "copy_blocks: pools of different contexts");
-  if (src->page_bytes != dst->page_bytes || src->desc.num_layers != dst->desc.num_layers)
-    return fail(EMM_ERR_LENGTH, "copy_blocks: pools differ in page size (%lld vs %lld) or layers (%d vs %d)",
+  if (src->page_bytes != dst->page_bytes || src->desc.num_layers != dst->desc.num_layers ||
+      src->planes != dst->planes)
+    return fail(EMM_ERR_LENGTH, "copy_blocks: pools differ in page size (%lld vs %lld), layers (%d vs %d) or planes",
                 (long long)src->page_bytes, (long long)dst->page_bytes, src->desc.num_layers,
                 dst->desc.num_layers);
   if (n < 0) return fail(EMM_ERR_BAD_ARG, "copy_blocks: negative block count");
@@ -666,7 +699,7 @@ int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
   if (!d_src_ids || !d_dst_ids) return fail(EMM_ERR_BAD_ARG, "copy_blocks: null id table");
   return launch_page_copy(src->ctx, pool_side(src, d_src_ids), pool_side(dst, d_dst_ids), n, 0,
                           src->desc.num_layers, src->page_bytes, std::min(src->align, dst->align),
-                          src->device_local && dst->device_local, (cudaStream_t)stream);
+                          src->device_local && dst->device_local, (cudaStream_t)stream, src->planes);
 }
 
 int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed,
@@ -753,6 +786,7 @@ static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
                        const int64_t *d_slots, int32_t T, void *stream) {
   if (!pool) return fail(EMM_ERR_BAD_ARG, "append: null pool");
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
+  if (pool->planes != 2) return fail(EMM_ERR_BAD_ARG, "append: needs a KV pool (two planes)");
   if (T < 0) return fail(EMM_ERR_BAD_ARG, "append: negative token count");
   if (T == 0 || layer_count == 0) return EMM_OK;
   if (!d_key || !d_value || !d_slots) return fail(EMM_ERR_BAD_ARG, "append: null pointer");
@@ -981,7 +1015,8 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     return fail(EMM_ERR_TOO_LARGE, "gather_noalloc: %d block ids exceed the fixed maximum of %d", n,
                 EMM_NOALLOC_MAX_IDS);
   const int64_t page = (int64_t)desc->block_size * desc->num_kv_heads * desc->head_size * desc->elem_size;
-  const uint64_t want = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * (uint64_t)page;
+  const int planes = desc->num_planes == 1 ? 1 : 2;
+  const uint64_t want = (uint64_t)desc->num_layers * (uint64_t)planes * (uint64_t)n * (uint64_t)page;
   if (packed_bytes != want)
     return fail(EMM_ERR_LENGTH, "gather_noalloc: packed buffer holds %llu bytes, %d blocks need %llu",
                 (unsigned long long)packed_bytes, n, (unsigned long long)want);
@@ -994,7 +1029,8 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   NoAllocDevice *nd = nullptr;
   if (int rc = noalloc_setup(device, &nd)) return rc;
 
-  uint32_t align = std::min(pow2_align((uint64_t)desc->plane_stride), pow2_align((uint64_t)desc->block_stride));
+  uint32_t align = pow2_align((uint64_t)desc->block_stride);
+  if (planes == 2) align = std::min(align, pow2_align((uint64_t)desc->plane_stride));
   align = std::min(align, std::min(pow2_align((uint64_t)page), pow2_align((uint64_t)d_packed)));
   uint64_t layer_addr[EMM_NOALLOC_MAX_LAYERS];
   for (int l = 0; l < desc->num_layers; ++l) {
@@ -1025,8 +1061,9 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   a.src.block_stride = (uint64_t)desc->block_stride;
   a.src.ids = reinterpret_cast<const int32_t *>(d_ids);
   a.src.num_blocks = (uint32_t)desc->num_blocks;
-  a.dst = packed_side(d_packed, n, page);
+  a.dst = packed_side(d_packed, n, page, planes);
   a.n = (uint32_t)n;
+  a.plane_shift = planes == 2 ? 1u : 0u;
   a.layer_begin = 0;
   a.layer_count = (uint32_t)desc->num_layers;
   a.page_bytes = (uint32_t)page;
@@ -1041,7 +1078,7 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     const int per_sm = (lanes + warps - 1) / warps;
     a.chunk_bytes = (uint32_t)chunk;
     a.chunks_per_page = (uint32_t)((page + chunk - 1) / chunk);
-    a.total_chunks = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * a.chunks_per_page;
+    a.total_chunks = (uint64_t)desc->num_layers * (uint64_t)planes * (uint64_t)n * a.chunks_per_page;
     const int smem = (int)(warps * stages * chunk);
     if (smem > nd->max_smem_optin - 2048)
       return fail(EMM_ERR_BAD_ARG, "gather_noalloc: ring does not fit shared memory");
@@ -1056,7 +1093,7 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     int64_t chunk = std::min<int64_t>(65536, page);
     a.chunk_bytes = (uint32_t)chunk;
     a.chunks_per_page = (uint32_t)((page + chunk - 1) / chunk);
-    a.total_chunks = (uint64_t)desc->num_layers * 2ull * (uint64_t)n * a.chunks_per_page;
+    a.total_chunks = (uint64_t)desc->num_layers * (uint64_t)planes * (uint64_t)n * a.chunks_per_page;
     const int grid = (int)std::min<uint64_t>(a.total_chunks, (uint64_t)nd->sm_count * 4);
     if (align >= 8) emm::page_copy_ldg<uint2, 2><<<grid, 256, 0, st>>>(a);
     else if (align >= 4) emm::page_copy_ldg<uint32_t, 2><<<grid, 256, 0, st>>>(a);

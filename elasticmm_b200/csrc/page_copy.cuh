@@ -2,7 +2,8 @@
 // block copy (compaction / swap) and direct stores into a peer GPU's pool.
 //
 // A work item ("chunk") is a run of at most `chunk_bytes` bytes inside one
-// page, a page being one block of one plane (K or V) of one layer. Chunks are
+// page, a page being one block of one plane (K or V; a block pool has a
+// single plane) of one layer. Chunks are
 // numbered with the chunk-in-page index fastest, then the block position i in
 // the table, then the plane, then the layer, so that neighbouring CTAs touch
 // neighbouring bytes of the packed side and the table is read once per page.
@@ -16,8 +17,8 @@
 //   * page_copy_bulk: each warp's lane 0 drives a ring of shared-memory
 //     buffers with cp.async.bulk (global -> shared, completion on an
 //     mbarrier) and cp.async.bulk (shared -> global, bulk groups). No data
-//     passes through registers, so a 128-thread CTA keeps >=96 KiB of loads in
-//     flight per SM.
+//     passes through registers; two to eight lanes per SM keep 32-64 KiB of
+//     loads in flight, which is where B200's HBM throughput peaks.
 //   * page_copy_ldg<V, U>: vector loads/stores through registers; also the
 //     path for geometries whose pages are not 16-byte granular, and for
 //     destinations that are not ordinary device memory of this GPU.
@@ -46,12 +47,13 @@ struct PageCopyArgs {
   CopySide src;
   CopySide dst;
   uint32_t n;                // table length
+  uint32_t plane_shift;      // 1: K and V planes per layer; 0: single-plane block pool
   uint32_t layer_begin;      // first layer of the pools to move
   uint32_t layer_count;      // number of layers to move
   uint32_t page_bytes;       // bytes per page
   uint32_t chunk_bytes;      // bytes per chunk (multiple of the vector width)
   uint32_t chunks_per_page;  // ceil(page_bytes / chunk_bytes)
-  uint64_t total_chunks;     // layer_count * 2 * n * chunks_per_page
+  uint64_t total_chunks;     // layer_count * planes * n * chunks_per_page
   int *status;               // [0] = sticky status code, [1..2] = detail (lo, hi)
 };
 
@@ -83,9 +85,9 @@ __device__ __forceinline__ ChunkAddr decode_chunk(const PageCopyArgs &a, uint64_
   uint32_t c = (uint32_t)(g - page * a.chunks_per_page);
   uint64_t t = page / a.n;
   uint32_t i = (uint32_t)(page - t * a.n);
-  uint32_t p = (uint32_t)(t & 1);
-  uint32_t l = a.layer_begin + (uint32_t)(t >> 1);  // index into the pools' layer arrays
-  uint32_t lrel = (uint32_t)(t >> 1);               // index on a linear (packed) side
+  uint32_t p = (uint32_t)(t & a.plane_shift);                   // plane_shift is 0 or 1: also the plane mask
+  uint32_t lrel = (uint32_t)(t >> a.plane_shift);               // index on a linear (packed) side
+  uint32_t l = a.layer_begin + lrel;                            // index into the pools' layer arrays
 
   ChunkAddr r;
   uint32_t off = c * a.chunk_bytes;

@@ -162,6 +162,41 @@ class V0KVTransferManager:
         self._account(elapsed, res.get("bytes", 0), len(src_blocks))
         return True
 
+    async def transfer_vision_embeddings(self, request_id: str, src_stage: str, src_worker_id: int,
+                                         src_blocks: List[int], dst_stage: str, dst_worker_id: int,
+                                         dst_blocks: List[int]) -> bool:
+        """Encode -> prefill hand-off of a request's vision embeddings, with the reference's
+        stage-keyed signature (elasticmm/engine/v0/kv_transfer.py:264-300). Workers are found through
+        the coordinator's (stage, worker_id) -> rank map. A request-keyed embedding is handed over
+        whole (:727-730); otherwise the block lists move through the block cache
+        (elasticmm/engine/v0/nccl_transfer.py:295-368)."""
+        if self.nccl_coordinator is None:
+            return False
+        src = self.worker_registry.get(self.nccl_coordinator.get_rank(self._normalize_stage(src_stage), src_worker_id))
+        dst = self.worker_registry.get(self.nccl_coordinator.get_rank(self._normalize_stage(dst_stage), dst_worker_id))
+        if src is None or dst is None:
+            return False
+        start = time.perf_counter()
+        try:
+            if src.ve_cache is not None and request_id in src.ve_cache:
+                data = src.extract_vision_blocks(request_id)
+                if dst.ve_cache is None:
+                    dst.init_ve_cache()
+                dst.write_vision_blocks(request_id, data if data.device == dst.device else data.to(dst.device))
+            else:
+                if len(src_blocks) != len(dst_blocks):
+                    return False
+                data = src.extract_ve_blocks(src_blocks)
+                dst.write_ve_blocks(dst_blocks, data if data.device == dst.device else data.to(dst.device))
+            torch.cuda.synchronize(dst.device)
+        except Exception as e:
+            self.last_result = {"error": f"{type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+            return False
+        self.transfer_count += 1
+        self.last_result = {"bytes": data.numel() * data.element_size(), "blocks": len(src_blocks),
+                            "elapsed": time.perf_counter() - start}
+        return True
+
     def transfer_many(self, plan: MigrationPlan) -> bool:
         """Moves a whole plan: one table per (source, sink) pair.
 

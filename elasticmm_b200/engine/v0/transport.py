@@ -121,6 +121,7 @@ class MigrationPlan:
 
     def __init__(self, transfers: Sequence[Transfer] = ()):
         self.transfers: List[Transfer] = []
+        self._tables = {}
         for t in transfers:
             self.add(t)
 
@@ -128,6 +129,7 @@ class MigrationPlan:
         if t.src_rank == t.dst_rank:
             raise ValueError(f"{t.request_id}: source and sink rank are both {t.src_rank}")
         self.transfers.append(t)
+        self._tables: Dict[Tuple[int, int], Tuple[List[int], List[int]]] = {}  # derived data is rebuilt lazily
 
     def pairs(self) -> List[Tuple[int, int]]:
         """(src, dst) pairs in a fixed order every rank agrees on."""
@@ -151,12 +153,16 @@ class MigrationPlan:
 
     def tables(self, src_rank: int, dst_rank: int) -> Tuple[List[int], List[int]]:
         """Concatenated (src_blocks, dst_blocks) of one pair, in plan order."""
+        cached = self._tables.get((src_rank, dst_rank))
+        if cached is not None:
+            return cached
         src: List[int] = []
         dst: List[int] = []
         for t in self.transfers:
             if t.src_rank == src_rank and t.dst_rank == dst_rank:
                 src += t.src_blocks
                 dst += t.dst_blocks
+        self._tables[(src_rank, dst_rank)] = (src, dst)
         return src, dst
 
     def outgoing(self, rank: int) -> List[int]:

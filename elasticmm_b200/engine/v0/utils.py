@@ -86,6 +86,30 @@ class KVTransferMetrics:
         self.kv_transfer_times.append(float(transfer_time_sec))
         self.kv_transfer_sizes.append(int(num_blocks))
 
+    def gain_cost_params(self) -> Dict[str, float]:
+        """The two keys the calibration derives from KV-transfer samples
+        (examples/calibrate_gain_cost.py:612-640): `migration_cost` = mean seconds per
+        transfer, `kv_transfer_bandwidth` = blocks per second."""
+        kv = self.get_stats().get("kv_transfer")
+        if not kv:
+            return {}
+        return {"migration_cost": kv["avg_time_sec"], "kv_transfer_bandwidth": kv["bandwidth_blocks_per_sec"]}
+
+    def update_gain_cost_file(self, path: str = "gain_cost_params.json") -> Dict[str, Any]:
+        """Merges the measured migration cost into the JSON file that
+        GainCostConfig loads (elasticmm/core/gain_cost_config.py:58-87); other keys are kept."""
+        import json
+        import os
+
+        params: Dict[str, Any] = {}
+        if os.path.exists(path):
+            with open(path) as f:
+                params = json.load(f)
+        params.update(self.gain_cost_params())
+        with open(path, "w") as f:
+            json.dump(params, f, indent=2, sort_keys=True)
+        return params
+
     def get_stats(self) -> Dict[str, Any]:
         stats: Dict[str, Any] = {"stage": self.stage_name}
         if self.kv_transfer_times:

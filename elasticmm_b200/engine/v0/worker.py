@@ -66,6 +66,10 @@ class V0Worker:
         self.pool: Optional[KVPool] = None
         self.swap_pool: Optional[KVPool] = None
         self.peer_pools: Dict[int, KVPool] = {}
+        self.ve_cache: Optional[Dict[str, torch.Tensor]] = None
+        self.ve_blocks: Optional[torch.Tensor] = None
+        self.ve_pool: Optional[KVPool] = None
+        self._peer_streams: Dict[int, torch.cuda.Stream] = {}
         self.swap_in_stream = torch.cuda.Stream(self.device)
         self.swap_out_stream = torch.cuda.Stream(self.device)
         self.swap_event_table: Dict[str, torch.cuda.Event] = {}
@@ -141,6 +145,54 @@ class V0Worker:
             "head_size": pool.head_size,
             "dtype": str(pool.dtype).split(".")[-1],
         }
+
+    # -- vision embeddings (elasticmm/engine/v0/worker.py:1007-1060) --------------
+    def init_ve_cache(self) -> None:
+        """Request-keyed embedding store, as the reference keeps it (a dict of tensors)."""
+        self.ve_cache = {}
+
+    def extract_vision_blocks(self, request_id: str) -> torch.Tensor:
+        if self.ve_cache is None:
+            raise RuntimeError("Vision embedding cache not initialized")
+        if request_id not in self.ve_cache:
+            raise KeyError(f"Request {request_id} not found in vision cache")
+        return self.ve_cache[request_id]
+
+    def write_vision_blocks(self, request_id: str, ve_data: torch.Tensor) -> None:
+        if self.ve_cache is None:
+            raise RuntimeError("Vision embedding cache not initialized")
+        self.ve_cache[request_id] = ve_data
+
+    def get_ve_cache_keys(self) -> List[str]:
+        return list(self.ve_cache.keys()) if self.ve_cache else []
+
+    def get_ve_shape(self, request_id: str):
+        if self.ve_cache and request_id in self.ve_cache:
+            return tuple(self.ve_cache[request_id].shape)
+        return None
+
+    def bind_ve_block_cache(self, ve_blocks: torch.Tensor) -> None:
+        """Adopts a block cache [blocks, embed_tokens, embed_dim], the form the
+        legacy transfer manager moves by block index
+        (elasticmm/engine/v0/nccl_transfer.py:295-368)."""
+        self.ve_blocks = ve_blocks
+        self.ve_pool = KVPool([ve_blocks], self.ctx)
+
+    def extract_ve_blocks(self, block_indices: List[int]) -> torch.Tensor:
+        """[n, embed_tokens, embed_dim]: the stacked source blocks, one launch."""
+        if self.ve_pool is None:
+            raise RuntimeError("Vision embedding cache not initialized")
+        n = len(block_indices)
+        packed = self.ve_pool.gather(block_indices)
+        return packed.view(n, self.ve_pool.block_size, self.ve_pool.head_size)
+
+    def write_ve_blocks(self, block_indices: List[int], ve_data: torch.Tensor) -> None:
+        if self.ve_pool is None:
+            raise RuntimeError("Vision embedding cache not initialized")
+        n = len(block_indices)
+        assert ve_data.shape[0] == n, f"Block count mismatch: {ve_data.shape[0]} vs {n}"
+        pool = self.ve_pool
+        self.ve_pool.scatter(block_indices, ve_data.reshape(1, 1, n, pool.block_size, 1, pool.head_size))
 
     # -- append and compaction (no counterpart in the reference's own code) ----
     def reshape_and_cache(self, key: torch.Tensor, value: torch.Tensor,
@@ -381,7 +433,7 @@ class V0Worker:
     def migrate(self, plan: MigrationPlan, method: str = "peer") -> Dict[str, Any]:
         """Runs this rank's part of a migration plan; every rank in the plan calls it.
 
-        method "peer": one direct-store launch per sink, then a barrier.
+        method "peer": one direct-store launch per sink, each on its own stream, then a barrier.
         method "nccl": per pair, the staged pipeline of p2p_send_kv / p2p_recv_kv;
         every rank walks the pairs in the plan's one global order (sources
         start at different sinks), which rules out a circular wait.
@@ -390,12 +442,26 @@ class V0Worker:
         pool = self._require_pool()
         moved = 0
         if method == "peer":
-            for dst in plan.outgoing(rank):
+            # One stream per sink: the pushes are link-bound and run side by side, so a source's
+            # egress stays busy whichever sink is momentarily the slower one.
+            main = torch.cuda.current_stream(self.device)
+            used = []
+            for src, dst in plan.ordered_pairs():
+                if src != rank:
+                    continue
                 src_ids, dst_ids = plan.tables(rank, dst)
-                res = self.p2p_push_kv(dst, src_ids, dst_ids)
+                stream = self._peer_streams.get(dst)
+                if stream is None:
+                    stream = self._peer_streams[dst] = torch.cuda.Stream(self.device)
+                stream.wait_stream(main)
+                with torch.cuda.stream(stream):
+                    res = self.p2p_push_kv(dst, src_ids, dst_ids)
+                used.append(stream)
                 if "error" in res:
                     return res
                 moved += res["blocks"]
+            for stream in used:
+                main.wait_stream(stream)
             torch.cuda.synchronize(self.device)
             rc, _ = self.ctx.status()
             dist.barrier(group=self.process_group)

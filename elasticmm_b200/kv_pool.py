@@ -142,7 +142,10 @@ class KVPool:
     """A paged KV pool known to the library.
 
     `layers` are the L per-layer tensors of logical shape [2, NB, BS, H, D]
-    with the innermost dimension contiguous. For a pool that is not torch
+    with the innermost dimension contiguous, or, for a single-plane block pool
+    such as the vision-embedding block cache
+    (elasticmm/engine/v0/nccl_transfer.py:295-368), tensors [NB, rows, cols];
+    packed buffers of a block pool are [L, 1, n, rows, 1, cols]. For a pool that is not torch
     memory (a peer GPU's pool mapped by Context.ipc_open, a pinned host pool)
     use `KVPool.from_pointers`.
     """
@@ -152,13 +155,14 @@ class KVPool:
         if not layers:
             raise ValueError("a pool needs at least one layer tensor")
         first = layers[0]
-        if first.dim() != 5 or first.shape[0] != 2:
-            raise ValueError(f"layer tensors must be [2, NB, BS, H, D], got {tuple(first.shape)}")
+        block_pool = first.dim() == 3  # [NB, rows, cols]: a single-plane block pool (vision embeddings)
+        if not block_pool and (first.dim() != 5 or first.shape[0] != 2):
+            raise ValueError(f"layer tensors must be [2, NB, BS, H, D] or [NB, rows, cols], got {tuple(first.shape)}")
         for t in layers:
             if t.shape != first.shape or t.dtype != first.dtype or t.stride() != first.stride():
                 raise ValueError("all layer tensors must share shape, dtype and strides")
-            if t.stride(4) != 1:
-                raise ValueError("head_dim must be contiguous")
+            if t.stride(-1) != 1:
+                raise ValueError("the innermost dimension must be contiguous")
         device = first.device
         if device.type == "cuda":
             self.ctx = ctx or get_context(device)
@@ -167,12 +171,19 @@ class KVPool:
                 raise ValueError("a host pool must be pinned and needs an explicit Context")
             self.ctx = ctx
         e = first.element_size()
-        desc = _lib.PoolDesc(
-            num_layers=len(layers), num_blocks=first.shape[1], block_size=first.shape[2],
-            num_kv_heads=first.shape[3], head_size=first.shape[4], elem_size=e,
-            plane_stride=first.stride(0) * e, block_stride=first.stride(1) * e,
-            token_stride=first.stride(2) * e, head_stride=first.stride(3) * e,
-        )
+        if block_pool:
+            desc = _lib.PoolDesc(
+                num_layers=len(layers), num_blocks=first.shape[0], block_size=first.shape[1], num_kv_heads=1,
+                head_size=first.shape[2], elem_size=e, plane_stride=0, block_stride=first.stride(0) * e,
+                token_stride=first.stride(1) * e, head_stride=first.shape[2] * e, num_planes=1, reserved=0,
+            )
+        else:
+            desc = _lib.PoolDesc(
+                num_layers=len(layers), num_blocks=first.shape[1], block_size=first.shape[2],
+                num_kv_heads=first.shape[3], head_size=first.shape[4], elem_size=e,
+                plane_stride=first.stride(0) * e, block_stride=first.stride(1) * e,
+                token_stride=first.stride(2) * e, head_stride=first.stride(3) * e, num_planes=2, reserved=0,
+            )
         self._layers = layers  # keeps the memory alive
         self.dtype = first.dtype
         self._init_handle(desc, [t.data_ptr() for t in layers])
@@ -202,6 +213,7 @@ class KVPool:
         self.num_kv_heads = desc.num_kv_heads
         self.head_size = desc.head_size
         self.elem_size = desc.elem_size
+        self.num_planes = 1 if desc.num_planes == 1 else 2
         self.page_bytes = int(lib.emm_pool_page_bytes(handle))
         self._append_sigs: Dict[tuple, int] = {}
         self._emm_append = lib.emm_append
@@ -220,17 +232,17 @@ class KVPool:
 
     def block_bytes(self) -> int:
         """Bytes of one block over all layers, K and V."""
-        return 2 * self.num_layers * self.page_bytes
+        return self.num_planes * self.num_layers * self.page_bytes
 
     def packed_bytes(self, n: int, layer_count: Optional[int] = None) -> int:
         lc = self.num_layers if layer_count is None else layer_count
-        return lc * 2 * n * self.page_bytes
+        return lc * self.num_planes * n * self.page_bytes
 
     def packed_shape(self, n: int, layer_count: Optional[int] = None) -> Tuple[int, ...]:
         lc = self.num_layers if layer_count is None else layer_count
         if self.head_major:
-            return (lc, 2, n, self.num_kv_heads, self.block_size, self.head_size)
-        return (lc, 2, n, self.block_size, self.num_kv_heads, self.head_size)
+            return (lc, self.num_planes, n, self.num_kv_heads, self.block_size, self.head_size)
+        return (lc, self.num_planes, n, self.block_size, self.num_kv_heads, self.head_size)
 
     def _logical(self, packed: torch.Tensor) -> torch.Tensor:
         """[.., n, BS, H, D] view of a packed buffer, whatever the page order."""
@@ -242,7 +254,7 @@ class KVPool:
                                          device=self.device))
 
     def _packed_ptr(self, packed: torch.Tensor, n: int, layer_count: int) -> Tuple[int, int]:
-        want = (layer_count, 2, n, self.block_size, self.num_kv_heads, self.head_size)
+        want = (layer_count, self.num_planes, n, self.block_size, self.num_kv_heads, self.head_size)
         if tuple(packed.shape) != want:
             raise ValueError(f"packed tensor has shape {tuple(packed.shape)}, expected {want}")
         if packed.dtype != self.dtype:

@@ -70,6 +70,8 @@ typedef struct emm_pool_desc {
   int64_t block_stride; /* bytes between consecutive blocks of a plane */
   int64_t token_stride; /* bytes between consecutive tokens of a block */
   int64_t head_stride;  /* bytes between consecutive heads of a token */
+  int32_t num_planes;   /* 2 for a KV pool (K plane, V plane); 1 for a single-plane block pool; 0 means 2 */
+  int32_t reserved;     /* must be 0 */
 } emm_pool_desc;
 
 /* Copy-kernel families, for emm_ctx_set_option(ctx, EMM_OPT_COPY_VARIANT, v). */
@@ -121,6 +123,14 @@ int emm_pool_desc_nhd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, 
 /* Same geometry with heads before tokens inside a block: [2, NB, H, BS, D]. */
 int emm_pool_desc_hnd(emm_pool_desc *desc, int L, int NB, int BS, int H, int D, int elem_size);
 
+/* Single-plane block pool [NB, rows, cols] per layer, e.g. the vision-embedding
+ * block cache [blocks, embed_tokens, embed_dim] that
+ * V0NCCLTransferManager.transfer_vision_embeddings gathers and scatters
+ * (elasticmm/engine/v0/nccl_transfer.py:295-368). A block is one page of
+ * rows*cols*elem_size bytes; the packed buffer is [L, 1, n, page]. Gather,
+ * scatter and block copy apply; append does not. */
+int emm_pool_desc_blocks(emm_pool_desc *desc, int L, int NB, int rows, int cols, int elem_size);
+
 /* `layer_ptrs` is a HOST array of L device (or device-visible) base
  * addresses; the library keeps a device copy. A single 6-D tensor
  * [L, 2, NB, BS, H, D] (elasticmm/engine/v0/nccl_transfer.py:215,241-244) is
@@ -138,7 +148,8 @@ int64_t emm_pool_page_bytes(const emm_pool *pool);
 
 /* Gather: packed[l][p][i] = pool[l][p][ids[i]] for all layers and both
  * planes, one launch. `d_ids` is a DEVICE int32 array of n block ids.
- * `packed_bytes` must equal L*2*n*page. Replaces the L index launches plus
+ * `packed_bytes` must equal L*planes*n*page (planes = 2 for a KV pool).
+ * Replaces the L index launches plus
  * torch.stack of V0Worker.extract_kv_blocks
  * (elasticmm/engine/v0/worker.py:578-610) and the gather half of p2p_send_kv
  * (:676-678) and of V0NCCLTransferManager.transfer_kv_cache_blocks

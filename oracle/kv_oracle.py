@@ -107,6 +107,20 @@ def copy_blocks(src_cache: Sequence[torch.Tensor], dst_cache: Sequence[torch.Ten
     write_kv_blocks(dst_cache, dst_ids, extract_kv_blocks(src_cache, src_ids))
 
 
+def transfer_vision_blocks(src_cache: torch.Tensor, dst_cache: torch.Tensor, src_blocks: Sequence[int],
+                           dst_blocks: Sequence[int]) -> torch.Tensor:
+    """elasticmm/engine/v0/nccl_transfer.py:328-363 on a block cache
+    [blocks, embed_tokens, embed_dim]: stack the source blocks, flatten (the
+    message), reshape on the sink and write block by block. Restated from the
+    source (the reference function needs a process group)."""
+    ve_data = torch.stack([src_cache[b] for b in src_blocks], dim=0)
+    flat = ve_data.flatten()
+    recv = flat.view(len(dst_blocks), src_cache.shape[1], src_cache.shape[2])
+    for i, b in enumerate(dst_blocks):
+        dst_cache[b] = recv[i]
+    return recv
+
+
 # ---------------------------------------------------------------------------
 # append (parity unpinned, see the module docstring)
 # ---------------------------------------------------------------------------

@@ -14,6 +14,8 @@ VARIANTS = [
     dict(variant=_lib.COPY_LDG, chunk_bytes=2048, ldg_unroll=1),
     dict(variant=_lib.COPY_LDG, chunk_bytes=65536, ldg_unroll=8),
 ]
+BULK_DEFAULT = VARIANTS[0]
+LDG_DEFAULT = next(v for v in VARIANTS if v["variant"] == _lib.COPY_LDG)
 DEFAULTS = dict(variant=_lib.COPY_AUTO, chunk_bytes=0, stages=2, warps=0, ctas_per_sm=0, ldg_unroll=2, max_ctas=0)
 
 

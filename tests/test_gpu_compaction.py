@@ -4,13 +4,13 @@ import torch
 
 from elasticmm_b200 import KVPool, get_context
 from elasticmm_b200.engine.v0 import Request, V0BlockManager, V0Worker
-from gpu_util import VARIANTS, assert_clean, configure, pools_equal, to_gpu, vid
+from gpu_util import BULK_DEFAULT, LDG_DEFAULT, VARIANTS, assert_clean, configure, pools_equal, to_gpu, vid
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("opts", [VARIANTS[0], VARIANTS[4]], ids=vid)
+@pytest.mark.parametrize("opts", [BULK_DEFAULT, LDG_DEFAULT], ids=vid)
 def test_evict_then_compact_matches_oracle(opts):
     """70B-shaped pages (8 KV heads, bf16) on a reduced pool: fill to ~85 %,
     evict the 30 % least recently used requests, compact."""

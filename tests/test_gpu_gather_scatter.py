@@ -8,7 +8,7 @@ import torch
 
 import cases
 from elasticmm_b200 import EmmError, KVPool, _lib, get_context
-from gpu_util import VARIANTS, assert_clean, configure, pools_equal, to_gpu, vid
+from gpu_util import BULK_DEFAULT, LDG_DEFAULT, VARIANTS, assert_clean, configure, pools_equal, to_gpu, vid
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu
@@ -52,7 +52,7 @@ def test_golden_cases(ctx, case, opts):
 
 
 @pytest.mark.parametrize("case", [cases.KV_CASES[0], cases.KV_CASES[4], cases.KV_CASES[10]], ids=lambda c: c["name"])
-@pytest.mark.parametrize("opts", [VARIANTS[0], VARIANTS[4]], ids=vid)
+@pytest.mark.parametrize("opts", [BULK_DEFAULT, LDG_DEFAULT], ids=vid)
 def test_device_tables_layer_ranges_and_block_copy(ctx, case, opts):
     configure(ctx, **opts)
     src_cpu, dst_cpu = cases.build_pools(case)
@@ -79,7 +79,7 @@ def test_device_tables_layer_ranges_and_block_copy(ctx, case, opts):
     assert pools_equal(dst2.layers, dst_cpu)
 
 
-@pytest.mark.parametrize("opts", [VARIANTS[0], VARIANTS[4]], ids=vid)
+@pytest.mark.parametrize("opts", [BULK_DEFAULT, LDG_DEFAULT], ids=vid)
 def test_head_major_pool_and_single_6d_tensor(ctx, opts):
     configure(ctx, **opts)
     L, NB, BS, H, D = 3, 10, 16, 4, 32
@@ -129,7 +129,7 @@ def test_errors_are_status_codes_not_faults(ctx):
         src.copy_blocks(src, [1, 2], [2, 5])    # block 2 is both read and written
     assert e.value.status == _lib.ERR_OVERLAP
     # device tables are checked by the kernel: the bad page is skipped, the rest is copied
-    for opts in (VARIANTS[0], VARIANTS[4]):
+    for opts in (BULK_DEFAULT, LDG_DEFAULT):
         configure(ctx, **opts)
         bad = torch.tensor([5, 99, 1, -3], dtype=torch.int32, device="cuda")
         out = torch.full((case["L"], 2, 4, case["BS"], case["H"], case["D"]), 7.0, dtype=torch.float16, device="cuda")

@@ -221,3 +221,23 @@ def test_migration_plan_grouping_and_order():
     dup = MigrationPlan([Transfer("a", 0, 2, (1,), (5,)), Transfer("b", 1, 2, (1,), (5,))])
     with pytest.raises(ValueError, match="assigned twice"):
         dup.validate(lambda r: 10)
+
+
+def test_metrics_feed_the_gain_cost_file(tmp_path):
+    """KV-transfer samples -> the keys the reference's calibration writes and GainCostConfig reads."""
+    from elasticmm_b200.engine.v0 import KVTransferMetrics
+
+    m = KVTransferMetrics("decoding", block_bytes=1 << 20)
+    assert m.gain_cost_params() == {} and "kv_transfer" not in m.get_stats()
+    for t, n in [(0.002, 15), (0.004, 45), (0.003, 30)]:
+        m.record_kv_transfer(transfer_time_sec=t, num_blocks=n)
+    kv = m.get_stats()["kv_transfer"]
+    assert kv["avg_time_sec"] == pytest.approx(0.003) and kv["avg_blocks"] == 30
+    assert kv["bandwidth_blocks_per_sec"] == pytest.approx(90 / 0.009)
+    assert kv["bandwidth_gb_per_sec"] == pytest.approx(90 * (1 << 20) / 0.009 / 1e9)
+    path = tmp_path / "gain_cost_params.json"
+    path.write_text(json.dumps({"preemption_penalty": 0.004, "migration_cost": 0.1}))
+    merged = m.update_gain_cost_file(str(path))
+    assert merged == json.loads(path.read_text())
+    assert merged["migration_cost"] == pytest.approx(0.003) and merged["preemption_penalty"] == 0.004
+    assert merged["kv_transfer_bandwidth"] == pytest.approx(10000.0)

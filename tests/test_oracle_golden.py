@@ -126,3 +126,14 @@ def test_block_tables_restatement_fragments_like_the_reference():
     bt.allocate("d", 30)
     assert bt.table["d"] == [7, 8, 9, 10, 11, 0, 1, 2]  # tail first, then the freed ids
     assert kv_oracle.slot_mapping_from_table(bt.table["d"], [0, 5, 21], 4) == [28, 33, 1]
+
+
+def test_vision_block_transfer_restatement():
+    g = torch.Generator().manual_seed(2)
+    src = torch.randn(12, 4, 8, generator=g).to(torch.bfloat16)
+    dst = torch.zeros(9, 4, 8, dtype=torch.bfloat16)
+    recv = kv_oracle.transfer_vision_blocks(src, dst, [7, 0, 11], [2, 8, 5])
+    assert recv.shape == (3, 4, 8)
+    for s, d in zip([7, 0, 11], [2, 8, 5]):
+        assert kv_oracle.bit_equal(dst[d], src[s])
+    assert torch.count_nonzero(dst[[0, 1, 3, 4, 6, 7]]) == 0
