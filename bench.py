@@ -7,7 +7,7 @@ One "step" migrates every request of the workload once.
   N = 1   BASELINE config 1 geometry (Llama-7B-shaped pool, fp16): each request is
           gathered from pool A into a contiguous buffer and scattered into pool B
           under an independent block table, in waves that fit the 2048-block pool.
-  N = 2   BASELINE config 3 (Qwen2.5-VL-7B-shaped pool, bf16): rank 0 -> rank 1.
+  N = 2   BASELINE config 3 (Qwen2.5-VL-7B-shaped pool, bf16): rank 0 -> rank 1 (the sink pulls).
   N = 4   BASELINE config 4 subset (LLaVA-13B-shaped pool, fp16): 2 sources -> 2 sinks.
   N = 8   BASELINE config 4: 2 sources -> 6 sinks, in waves bounded by the pools.
 For N > 1 launch under torchrun (one rank per GPU). The line's `value` is the
@@ -531,9 +531,8 @@ def bench_multi(args):
     worker.init_global_nccl()
     handles = [None] * world
     dist.all_gather_object(handles, (worker.get_ipc_handles(), worker.get_pool_desc()))
-    if is_src:
-        for peer in sinks:
-            worker.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
+    for peer in (sinks if is_src else sources):  # sources map sinks (push variant), sinks map sources (pull)
+        worker.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
     nxt = (rank + 1) % world  # ring neighbour, for the all-ranks exchange variant
     if nxt not in worker.peer_pools:
         worker.attach_peer_pool(nxt, handles[nxt][0], handles[nxt][1])
@@ -583,32 +582,45 @@ def bench_multi(args):
     total_blocks = sum(p.total_blocks() for p in plans)
     payload = total_blocks * block_bytes(w)
 
-    # device-resident tables per (wave, sink) for the sources
-    tables = []
+    # device-resident tables per wave, in the order this rank serves its peers: sinks hold
+    # (source, src ids, dst ids) for the pull path, sources hold (sink, ...) for the push variant
+    push_tables, pull_tables = [], []
     for plan in plans:
-        per = []
-        for s, d in plan.ordered_pairs():
-            if s == rank:
-                si, di = plan.tables(s, d)
-                per.append((d, worker.pool.upload_ids(si), worker.pool.upload_ids(di)))
-        tables.append(per)
+        pull = [(s,) + tuple(worker.pool.upload_ids(t) for t in plan.tables(s, rank)) for s in plan.pull_order(rank)]
+        push = [(d,) + tuple(worker.pool.upload_ids(t) for t in plan.tables(rank, d)) for d in plan.push_order(rank)]
+        pull_tables.append(pull)
+        push_tables.append(push)
 
     def barrier():
         dist.barrier()
 
-    streams = {d: torch.cuda.Stream(device) for d in sinks}
+    streams = {p: torch.cuda.Stream(device) for p in range(world)}
+    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
 
-    def step_peer():
+    def run_waves(tables, pull):
         main = torch.cuda.current_stream(device)
         for per in tables:
-            for d, si, di in per:  # one stream per sink: link-bound pushes run side by side
-                streams[d].wait_stream(main)
-                with torch.cuda.stream(streams[d]):
-                    worker.pool.copy_blocks(worker.peer_pools[d], si, di)
-            for d, _, _ in per:
-                main.wait_stream(streams[d])
+            if pull:
+                # all sources of this sink at once, grids capped to one CTA per SM in total (measured:
+                # uncapped side-by-side pulls halve the NVSwitch rate, capped ones run at link speed)
+                cap = max(24, sm_count // max(1, len(per))) if len(per) > 1 else None
+                for peer, si, di in per:
+                    streams[peer].wait_stream(main)
+                    with torch.cuda.stream(streams[peer]):
+                        worker.peer_pools[peer].copy_blocks(worker.pool, si, di, max_ctas=cap)
+                for peer, _, _ in per:
+                    main.wait_stream(streams[peer])
+            else:
+                for peer, si, di in per:  # one sink at a time, sources start at different sinks
+                    worker.pool.copy_blocks(worker.peer_pools[peer], si, di)
             torch.cuda.synchronize(device)
-            dist.barrier()  # wave boundary: the sinks may reuse their blocks only after every push landed
+            dist.barrier()  # wave boundary: blocks are reused only after every copy of the wave landed
+
+    def step_pull():
+        run_waves(pull_tables, True)
+
+    def step_push():
+        run_waves(push_tables, False)
 
     def step_nccl():
         for plan in plans:
@@ -617,7 +629,7 @@ def bench_multi(args):
             dist.barrier()
 
     # correctness gate: checksums of what landed against what was sent (last wave)
-    step_peer()
+    step_pull()
     sums = block_checksums(worker.pool.layers).cpu()
     all_sums = [None] * world
     dist.all_gather_object(all_sums, sums)
@@ -638,14 +650,18 @@ def bench_multi(args):
 
     l0 = worker.ctx.launch_count
     with ClockSampler(local) as clocks:
-        ms = max_ms(timed(step_peer, args.steps, args.warmup, device, barrier))
-    launches = worker.ctx.launch_count - l0 - args.warmup * sum(len(p) for p in tables)
+        ms = max_ms(timed(step_pull, args.steps, args.warmup, device, barrier))
+    launches = worker.ctx.launch_count - l0 - args.warmup * sum(len(p) for p in pull_tables)
     lt = torch.tensor([launches], device=device, dtype=torch.int64)
     dist.all_reduce(lt)
     value = payload * args.steps / (ms / 1e3) / 1e9
 
     nccl_steps = max(2, args.steps // 4)
     variants = {}
+    ms_p = max_ms(timed(step_push, nccl_steps, 2, device, barrier))
+    variants["peer_push"] = {"value": round(payload * nccl_steps / (ms_p / 1e3) / 1e9, 2), "unit": "GB/s",
+                             "ms_per_step": round(ms_p / nccl_steps, 3),
+                             "path": "sources store into the sinks' peer-mapped pools (same kernel, other direction)"}
     try:
         ms_n = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
         variants["nccl_staged"] = {"value": round(payload * nccl_steps / (ms_n / 1e3) / 1e9, 2), "unit": "GB/s",
@@ -654,15 +670,15 @@ def bench_multi(args):
     except Exception as e:
         variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
 
-    # Every rank a source and a sink at once (the rebalancing exchange): rank r stores the lower half of
-    # its pool into the upper half of rank r+1's pool. Run last among the device-resident variants because
+    # Every rank a source and a sink at once (the rebalancing exchange): rank r loads the lower half of
+    # rank r+1's pool into the upper half of its own. Run last among the device-resident variants because
     # it overwrites pool contents.
     half = w["NB"] // 2
     ring_src = worker.pool.upload_ids(torch.randperm(half, generator=torch.Generator().manual_seed(rank)).tolist())
     ring_dst = worker.pool.upload_ids((torch.randperm(half, generator=torch.Generator().manual_seed(50 + rank)) + half).tolist())
 
     def step_ring():
-        worker.pool.copy_blocks(worker.peer_pools[nxt], ring_src, ring_dst)
+        worker.peer_pools[nxt].copy_blocks(worker.pool, ring_src, ring_dst)
         torch.cuda.synchronize(device)
         dist.barrier()
 
@@ -671,14 +687,14 @@ def bench_multi(args):
     ring_bytes = world * half * block_bytes(w)
     variants["ring_exchange_all_ranks"] = {
         "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
-        "per_gpu_egress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
+        "per_gpu_ingress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
         "ms_per_step": round(ms_r / ring_steps, 3),
-        "path": "every rank stores half of its pool into the next rank's pool at the same time"}
+        "path": "every rank pulls half of the next rank's pool into its own at the same time"}
 
     # end to end through the worker API with host id lists (tables uploaded inside the timed region)
     def step_e2e():
         for plan in plans:
-            res = worker.migrate(plan, method="peer")
+            res = worker.migrate(plan, method="pull")
             assert "error" not in res, res
 
     e2e_steps = max(2, args.steps // 4)
@@ -694,23 +710,113 @@ def bench_multi(args):
             "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
                        "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(plans),
                        "payload_gib_per_step": round(payload / GIB, 2), "sources": sources, "sinks": sinks,
-                       "path": "one direct-store kernel per (source, sink), sinks served concurrently on separate "
-                               "streams: local loads, NVLink stores into the sink's peer-mapped pool", "l2": "inputs larger than L2",
+                       "path": "one direct-load kernel per (source, sink) launched by the sink, its sources side by "
+                               "side on separate streams with grids capped to one CTA per SM in total: NVLink loads "
+                               "from the source's peer-mapped pool, local stores", "l2": "inputs larger than L2",
                        "per_source_egress_gbs": round(per_src_gbs, 2),
                        "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
             "verified_bit_exact_checksum": verified,
             "roofline": {"bound": "nvlink", "achieved": round(per_src_gbs, 1), "peak": NVLINK_PEER_COPY_GBS,
                          "unit": "GB/s", "frac": round(per_src_gbs / NVLINK_PEER_COPY_GBS, 4), "traffic": None,
                          "peak_kind": "of measured peer copy per direction per GPU (900 nominal)",
-                         "frac_of_900_nominal": round(per_src_gbs / 900.0, 4), "kernel": "page_copy_ldg (peer stores)"},
+                         "frac_of_900_nominal": round(per_src_gbs / 900.0, 4), "kernel": "page_copy_ldg (peer loads)"},
             "e2e": {"value": round(payload * e2e_steps / (ms_e / 1e3) / 1e9, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16 * len(plans) * len(sources),
-                    "api": "V0Worker.migrate(plan, method='peer') with host id lists", "steps": e2e_steps},
+                    "api": "V0Worker.migrate(plan, method='pull') with host id lists", "steps": e2e_steps},
             "gpu_launches": int(lt.item()),
             "clocks": clocks.summary(),
             "variants": variants,
         }
         print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def probe_fabric(args):
+    """Peer-copy patterns over NVSwitch (N >= 2 ranks): one flow with different grid sizes, and with
+    N >= 4 two sources -> all other ranks as sinks, pulled side by side with full grids, with grids capped
+    to one CTA per SM in total, and one source at a time. One JSON line per pattern on rank 0. These
+    measurements fixed the schedule V0Worker.migrate uses."""
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import V0Worker
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    w = dict(WORKLOADS["llava13b_cfg4"], NB=1024)
+    n = 512  # blocks per flow: 6.25 GiB
+    worker = V0Worker(worker_id=rank, dtype=w["dtype"], device=device, global_rank=rank, world_size=world,
+                      kv_cache=gpu_pool(w, device, rank))
+    worker.init_global_nccl()
+    handles = [None] * world
+    dist.all_gather_object(handles, (worker.get_ipc_handles(), worker.get_pool_desc()))
+    for peer in range(world):
+        if peer != rank:
+            worker.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
+    g = torch.Generator().manual_seed(rank)
+    tabs = {p: (worker.pool.upload_ids(torch.randperm(w["NB"] // 2, generator=g)[:n].tolist()),
+                worker.pool.upload_ids((torch.randperm(w["NB"] // 2, generator=g)[:n] + w["NB"] // 2).tolist()))
+            for p in range(world)}
+    streams = {p: torch.cuda.Stream(device) for p in range(world)}
+    flow_bytes = n * block_bytes(w)
+
+    def run(name, ops, flows, cap=None, serial=False, iters=3):
+        """ops: [(kind, peer)] this rank runs; 'pull' loads peer -> here, 'push' stores here -> peer."""
+        def step():
+            main = torch.cuda.current_stream(device)
+            for kind, peer in ops:
+                st = main if serial else streams[peer]
+                if not serial:
+                    st.wait_stream(main)
+                with torch.cuda.stream(st):
+                    si, di = tabs[peer]
+                    if kind == "pull":
+                        worker.peer_pools[peer].copy_blocks(worker.pool, si, di, max_ctas=cap)
+                    else:
+                        worker.pool.copy_blocks(worker.peer_pools[peer], si, di, max_ctas=cap)
+            if not serial:
+                for _, peer in ops:
+                    main.wait_stream(streams[peer])
+        step()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            step()
+        b.record()
+        torch.cuda.synchronize(device)
+        ms = torch.tensor([a.elapsed_time(b) / iters], device=device, dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        if rank == 0:
+            print(json.dumps({"probe": name, "flows": flows, "ms": round(ms.item(), 3),
+                              "total_gbs": round(flows * flow_bytes / ms.item() / 1e6, 1)}))
+
+    for cap in (None, 74, 48, 37, 24):
+        run(f"one pull flow 1<-0, grid cap {cap}", [("pull", 0)] if rank == 1 else [], 1, cap=cap)
+        run(f"one push flow 0->1, grid cap {cap}", [("push", 1)] if rank == 0 else [], 1, cap=cap)
+    if world >= 4:
+        srcs, snks = [0, 1], list(range(2, world))
+        j = snks.index(rank) if rank in snks else 0
+        pulls = [("pull", s) for s in srcs] if rank in snks else []
+        run(f"pull 2->{len(snks)}, both sources at once, full grids", pulls, 2 * len(snks))
+        for cap in (120, 100, 74, 48):
+            run(f"pull 2->{len(snks)}, both sources at once, grid cap {cap} each", pulls, 2 * len(snks), cap=cap)
+        run(f"pull 2->{len(snks)}, one source at a time, rotated start",
+            [("pull", srcs[(j + k) % 2]) for k in range(2)] if rank in snks else [], 2 * len(snks), serial=True)
+        run(f"pull 2->{len(snks)}, one source at a time, same start", pulls, 2 * len(snks), serial=True)
+        pushes = [("push", d) for d in snks] if rank in srcs else []
+        run(f"push 2->{len(snks)}, all sinks at once, full grids", pushes, 2 * len(snks))
+        i = srcs.index(rank) if rank in srcs else 0
+        k0 = i * (len(snks) // 2)
+        run(f"push 2->{len(snks)}, one sink at a time, rotated start",
+            [("push", snks[(k0 + k) % len(snks)]) for k in range(len(snks))] if rank in srcs else [],
+            2 * len(snks), serial=True)
+        run("ring: every rank pulls from the next", [("pull", (rank + 1) % world)], world)
+        run("ring: every rank pushes to the next", [("push", (rank + 1) % world)], world)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -725,6 +831,8 @@ def main():
                     help="N=1: the same geometries on pools of a few GiB and 8 requests (the case profiled under ncu)")
     ap.add_argument("--skip-extras", action="store_true", help="N=1: skip the append and compaction objects")
     ap.add_argument("--skip-cpu", action="store_true", help="N=1: skip the CPU baseline leg")
+    ap.add_argument("--probe-fabric", action="store_true",
+                    help="N>1: measure peer-copy patterns over NVSwitch instead of the migration workload")
     ap.add_argument("--variant", type=int, default=None, help="copy kernel family (1 bulk, 2 ldg)")
     ap.add_argument("--chunk", type=int, default=None)
     ap.add_argument("--stages", type=int, default=None)
@@ -749,7 +857,9 @@ def main():
         torch.cuda.set_device(dev)
         get_context(dev).configure(variant=args.variant, chunk_bytes=args.chunk, stages=args.stages,
                                    warps=args.warps, ctas_per_sm=args.ctas_per_sm, ldg_unroll=args.unroll)
-    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+    if args.probe_fabric:
+        probe_fabric(args)
+    elif args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         bench_single(args)
     else:
         bench_multi(args)

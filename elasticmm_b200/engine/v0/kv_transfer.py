@@ -16,7 +16,7 @@ this process; otherwise this process performs its half (send or push on the
 source, receive on the sink) and the peer process performs the other half by
 making the same call.
 
-Added: TransferMethod.B200_PEER (direct stores into the sink's mapped pool)
+Added: TransferMethod.B200_PEER (direct loads from / stores into a peer-mapped pool)
 and `transfer_many(plan)`, which moves all requests of a role switch as one
 table per (source, sink) pair instead of one call per request
 (the reference serialises them, elasticmm/engine/v0/backend.py:674-718).
@@ -37,13 +37,16 @@ class TransferMethod(Enum):
     NCCL = "nccl"              # staged: pack -> NCCL send/recv -> unpack, pipelined by layer chunk
     P2P_COPY = "p2p_copy"      # extract on the source, write on the sink (both workers in this process)
     STAGED_COPY = "staged_copy"  # not implemented in the reference either (a sleep); refused here
-    B200_PEER = "b200_peer"    # one kernel: local loads, stores into the sink's peer-mapped pool
+    B200_PEER = "b200_peer"    # one kernel over peer-mapped pools: the sink loads (default) or the source stores
 
 
 class V0KVTransferManager:
     def __init__(self, transfer_method: TransferMethod = TransferMethod.P2P_COPY, nccl_coordinator=None,
                  enable_batching: bool = False, batch_size: int = 3, batch_timeout: float = 0.005,
-                 metrics_callback: Optional[Callable[..., None]] = None):
+                 metrics_callback: Optional[Callable[..., None]] = None, peer_direction: str = "pull"):
+        if peer_direction not in ("pull", "push"):
+            raise ValueError("peer_direction must be 'pull' or 'push'")
+        self.peer_direction = peer_direction  # B200_PEER: the sink loads (default) or the source stores
         self.transfer_method = transfer_method
         self.nccl_coordinator = nccl_coordinator
         self.enable_batching = enable_batching  # kept for signature parity; see transfer_many
@@ -124,17 +127,20 @@ class V0KVTransferManager:
                 return dst.p2p_coordinated_transfer_kv(None, src_rank, src_blocks, dst_blocks, timeout=10.0)
             return src.p2p_send_kv(dst_rank, src_blocks)
         if method == TransferMethod.B200_PEER:
-            if src is None:
-                return {"bytes": 0, "blocks": len(src_blocks), "passive": True}  # the sink does nothing
-            if dst is not None and dst_rank not in src.peer_pools:
-                # both pools in this process and on this GPU: direct block copy
-                src.pool.copy_blocks(dst.pool, src_blocks, dst_blocks)
-                res = {"bytes": len(src_blocks) * src.pool.block_bytes(), "blocks": len(src_blocks)}
+            if src is not None and dst is not None and src.device == dst.device:
+                src.pool.copy_blocks(dst.pool, src_blocks, dst_blocks)                    # both pools on this GPU
+                worker, res = src, {"bytes": len(src_blocks) * src.pool.block_bytes(), "blocks": len(src_blocks)}
+            elif self.peer_direction == "pull":
+                if dst is None:  # the sink does the copy; the source's half of the call is a no-op
+                    return {"bytes": 0, "blocks": len(src_blocks), "passive": True}
+                worker, res = dst, dst.p2p_pull_kv(src_rank, src_blocks, dst_blocks)      # sink loads over the link
             else:
-                res = src.p2p_push_kv(dst_rank, src_blocks, dst_blocks)
+                if src is None:
+                    return {"bytes": 0, "blocks": len(src_blocks), "passive": True}
+                worker, res = src, src.p2p_push_kv(dst_rank, src_blocks, dst_blocks)      # source stores over the link
             if "error" not in res:
-                torch.cuda.synchronize(src.device)
-                rc, _ = src.ctx.status()
+                torch.cuda.synchronize(worker.device)
+                rc, _ = worker.ctx.status()
                 if rc != 0:
                     return {"error": "device reported a bad block id", "bytes": 0, "blocks": 0}
             return res
@@ -201,11 +207,11 @@ class V0KVTransferManager:
         """Moves a whole plan: one table per (source, sink) pair.
 
         Every process that owns a rank named in the plan makes this call. With
-        B200_PEER the sources push and all ranks meet at a barrier; with NCCL
+        B200_PEER the sinks pull and all ranks meet at a barrier; with NCCL
         each pair runs the staged pipeline.
         """
         start = time.perf_counter()
-        method = "peer" if self.transfer_method in (TransferMethod.B200_PEER, TransferMethod.CUDA_IPC) else "nccl"
+        method = self.peer_direction if self.transfer_method in (TransferMethod.B200_PEER, TransferMethod.CUDA_IPC) else "nccl"
         if self.transfer_method not in (TransferMethod.B200_PEER, TransferMethod.CUDA_IPC, TransferMethod.NCCL):
             ok = all(self.transfer_kv_cache_sync(t.request_id, t.src_rank, t.dst_rank, list(t.src_blocks),
                                                  list(t.dst_blocks)) for t in plan.transfers)

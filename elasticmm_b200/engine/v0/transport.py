@@ -151,6 +151,29 @@ class MigrationPlan:
         step = lambda sd: (sinks.index(sd[1]) - sources.index(sd[0])) % m
         return sorted(pairs, key=lambda sd: (step(sd), sd[0], sd[1]))
 
+    def pull_order(self, sink: int) -> List[int]:
+        """Sources of `sink`, rotated so that sink number j lists source number j first.
+
+        A sink launches its pulls in this order (side by side, with capped grids);
+        the rotation spreads the first requests over the sources.
+        """
+        sinks = sorted({d for _, d in self.pairs()})
+        mine = sorted(s for s, d in self.pairs() if d == sink)
+        if not mine:
+            return []
+        k = sinks.index(sink) % len(mine)
+        return mine[k:] + mine[:k]
+
+    def push_order(self, source: int) -> List[int]:
+        """Sinks of `source` in the order it should push to them, one at a time
+        (the mirror image of pull_order: one flow per source, starts spread out)."""
+        sources = sorted({s for s, _ in self.pairs()})
+        mine = sorted(d for s, d in self.pairs() if s == source)
+        if not mine:
+            return []
+        k = (sources.index(source) * max(1, len(mine) // len(sources))) % len(mine)
+        return mine[k:] + mine[:k]
+
     def tables(self, src_rank: int, dst_rank: int) -> Tuple[List[int], List[int]]:
         """Concatenated (src_blocks, dst_blocks) of one pair, in plan order."""
         cached = self._tables.get((src_rank, dst_rank))

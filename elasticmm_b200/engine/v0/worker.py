@@ -66,10 +66,10 @@ class V0Worker:
         self.pool: Optional[KVPool] = None
         self.swap_pool: Optional[KVPool] = None
         self.peer_pools: Dict[int, KVPool] = {}
+        self._peer_streams: Dict[int, torch.cuda.Stream] = {}
         self.ve_cache: Optional[Dict[str, torch.Tensor]] = None
         self.ve_blocks: Optional[torch.Tensor] = None
         self.ve_pool: Optional[KVPool] = None
-        self._peer_streams: Dict[int, torch.cuda.Stream] = {}
         self.swap_in_stream = torch.cuda.Stream(self.device)
         self.swap_out_stream = torch.cuda.Stream(self.device)
         self.swap_event_table: Dict[str, torch.cuda.Event] = {}
@@ -429,44 +429,84 @@ class V0Worker:
             return {"error": str(e), "bytes": 0, "blocks": 0}
         return {"bytes": len(src_blocks) * pool.block_bytes(), "blocks": len(src_blocks)}
 
+    def p2p_pull_kv(self, src_rank: int, src_blocks: List[int], dst_blocks: List[int],
+                    max_ctas: Optional[int] = None) -> Dict[str, Any]:
+        """Pull KV blocks from the worker with global rank `src_rank` into this pool.
+
+        Same name, arguments and direction as the reference's receiver-driven
+        pull (elasticmm/engine/v0/worker.py:873-910, unused there). Here it is one
+        kernel on the SINK: loads over NVLink from the source's peer-mapped pool,
+        stores into the local blocks; no request message, no staging buffer, no
+        NCCL call. Loads over the link measured ~10 % faster than stores (785 vs
+        716 GB/s per direction), so this is the default direction. Asynchronous on
+        the current stream; the source may free its blocks once this stream has
+        completed. `max_ctas` caps the grid when several pulls run side by side.
+        """
+        if src_rank not in self.peer_pools:
+            return {"error": f"pool of rank {src_rank} is not mapped", "bytes": 0, "blocks": 0}
+        if len(src_blocks) != len(dst_blocks):
+            raise ValueError(f"Block count mismatch: src={len(src_blocks)}, dst={len(dst_blocks)}")
+        pool = self._require_pool()
+        try:
+            self.peer_pools[src_rank].copy_blocks(pool, src_blocks, dst_blocks, max_ctas=max_ctas)
+        except _lib.EmmError as e:
+            return {"error": str(e), "bytes": 0, "blocks": 0}
+        return {"bytes": len(src_blocks) * pool.block_bytes(), "blocks": len(src_blocks)}
+
     # -- plan-level migration -----------------------------------------------------
-    def migrate(self, plan: MigrationPlan, method: str = "peer") -> Dict[str, Any]:
+    def migrate(self, plan: MigrationPlan, method: str = "pull") -> Dict[str, Any]:
         """Runs this rank's part of a migration plan; every rank in the plan calls it.
 
-        method "peer": one direct-store launch per sink, each on its own stream, then a barrier.
-        method "nccl": per pair, the staged pipeline of p2p_send_kv / p2p_recv_kv;
-        every rank walks the pairs in the plan's one global order (sources
-        start at different sinks), which rules out a circular wait.
+        method "pull" (default; "peer" is an alias): each sink launches one
+        direct-load kernel per source, side by side with capped grids, then all
+        ranks meet at a barrier. method "push": each source launches one
+        direct-store kernel per sink instead, one sink at a time. method "nccl": per pair, the staged pipeline of
+        p2p_send_kv / p2p_recv_kv; every rank walks the pairs in the plan's one
+        global order (sources start at different sinks), which rules out a
+        circular wait.
         """
         rank = self.get_global_rank()
         pool = self._require_pool()
         moved = 0
         if method == "peer":
-            # One stream per sink: the pushes are link-bound and run side by side, so a source's
-            # egress stays busy whichever sink is momentarily the slower one.
+            method = "pull"
+        if method == "pull":
+            # A sink pulls from all its sources at once, one stream per source, with the grids capped
+            # so that the launches together hold at most one CTA per SM: measured on NVSwitch, two
+            # full-size pull kernels side by side halve the rate, two half-size ones run at full link
+            # speed, and a flow that is left alone still saturates the link with its share of CTAs.
+            peers = plan.pull_order(rank)
+            cap = max(24, self.ctx.sm_count // max(1, len(peers)))
             main = torch.cuda.current_stream(self.device)
             used = []
-            for src, dst in plan.ordered_pairs():
-                if src != rank:
-                    continue
-                src_ids, dst_ids = plan.tables(rank, dst)
-                stream = self._peer_streams.get(dst)
+            for peer in peers:
+                src_ids, dst_ids = plan.tables(peer, rank)
+                stream = self._peer_streams.get(peer)
                 if stream is None:
-                    stream = self._peer_streams[dst] = torch.cuda.Stream(self.device)
+                    stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
                 stream.wait_stream(main)
                 with torch.cuda.stream(stream):
-                    res = self.p2p_push_kv(dst, src_ids, dst_ids)
+                    res = self.p2p_pull_kv(peer, src_ids, dst_ids, max_ctas=cap if len(peers) > 1 else None)
                 used.append(stream)
                 if "error" in res:
                     return res
                 moved += res["blocks"]
             for stream in used:
                 main.wait_stream(stream)
+        elif method == "push":
+            # A source pushes to one sink at a time, sources starting at different sinks.
+            for peer in plan.push_order(rank):
+                src_ids, dst_ids = plan.tables(rank, peer)
+                res = self.p2p_push_kv(peer, src_ids, dst_ids)
+                if "error" in res:
+                    return res
+                moved += res["blocks"]
+        if method in ("pull", "push"):
             torch.cuda.synchronize(self.device)
             rc, _ = self.ctx.status()
             dist.barrier(group=self.process_group)
             if rc != _lib.OK:
-                return {"error": f"push failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+                return {"error": f"{method} failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
         elif method == "nccl":
             if plan.outgoing(rank) and plan.incoming(rank):
                 return {"error": "nccl migration needs each rank to be a pure source or a pure sink; "

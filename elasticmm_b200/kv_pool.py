@@ -48,6 +48,7 @@ class Context:
             handle = C.c_void_p()
             _lib.check(self._lib.emm_ctx_create(index, C.byref(handle)))
         self._h = handle
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # -- options ---------------------------------------------------------
     def set_option(self, option: int, value: int) -> None:
@@ -332,10 +333,21 @@ class KVPool:
             raise _lib.EmmError(_lib.ERR_DUPLICATE, "duplicate destination block id")
         return host
 
-    def copy_blocks(self, dst: "KVPool", src_ids: IdList, dst_ids: IdList) -> None:
-        """dst[l][p, dst_ids[i]] = self[l][p, src_ids[i]] with no staging buffer."""
+    def copy_blocks(self, dst: "KVPool", src_ids: IdList, dst_ids: IdList,
+                    max_ctas: Optional[int] = None) -> None:
+        """dst[l][p, dst_ids[i]] = self[l][p, src_ids[i]] with no staging buffer.
+
+        `max_ctas` caps this launch's grid (used when several link-bound copies
+        run side by side on different streams)."""
         if dst.ctx is not self.ctx:
             raise ValueError("both pools must belong to the same Context")
+        if max_ctas is not None:
+            before = self.ctx.get_option(_lib.OPT_MAX_CTAS)
+            self.ctx.set_option(_lib.OPT_MAX_CTAS, max_ctas)
+            try:
+                return self.copy_blocks(dst, src_ids, dst_ids)
+            finally:
+                self.ctx.set_option(_lib.OPT_MAX_CTAS, before)
         lib = self.ctx._lib
         st = C.c_void_p(_stream_ptr(self.device))
         dev_tables = isinstance(src_ids, torch.Tensor) and src_ids.is_cuda

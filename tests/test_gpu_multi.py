@@ -84,19 +84,30 @@ def _worker_main(rank, world, port, out_dir):
     for peer in range(world):
         if peer != rank:
             w.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
-    mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
-    mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
-    oks = [mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs]
-    results["peer_ok"] = all(oks)
-    dist.barrier()
-    if rank == 1:
-        results["peer_exact"] = same(w, expect(reqs))
-    dist.barrier()
+    for direction in ("pull", "push"):
+        if direction == "push":
+            w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+            handles = [None] * world
+            dist.all_gather_object(handles, (w.get_ipc_handles(), w.get_pool_desc()))
+            for peer in range(world):
+                if peer != rank:
+                    w.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
+        mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER, peer_direction=direction)
+        mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+        launches = w.ctx.launch_count
+        oks = [mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs]
+        results[f"peer_{direction}_ok"] = all(oks)
+        active = 1 if direction == "pull" else 0
+        results[f"peer_{direction}_launches_ok"] = (w.ctx.launch_count - launches) == (len(reqs) if rank == active else 0)
+        dist.barrier()
+        if rank == 1:
+            results[f"peer_{direction}_exact"] = same(w, expect(reqs))
+        dist.barrier()
 
     # 3. plan level, both methods, all requests as one table per pair
-    for method in ("peer", "nccl"):
+    for method in ("pull", "push", "nccl"):
         w2, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
-        if method == "peer":
+        if method != "nccl":
             h2 = [None] * world
             dist.all_gather_object(h2, (w2.get_ipc_handles(), w2.get_pool_desc()))
             for peer in range(world):
@@ -124,7 +135,7 @@ def _worker_main(rank, world, port, out_dir):
             w3.attach_peer_pool(peer, h3[peer][0], h3[peer][1])
     plan = MigrationPlan([Transfer(f"{rid}-{src}", src, 1 - src, tuple(s), tuple(d))
                           for src in (0, 1) for rid, s, d in _requests(3 + src)])
-    res = w3.migrate(plan, method="peer")
+    res = w3.migrate(plan, method="push")
     results["exchange_ok"] = "error" not in res
     dist.barrier()
     mine = [(rid, s, d) for rid, s, d in _requests(3 + (1 - rank))]
@@ -144,6 +155,6 @@ def test_two_gpu_migration_is_bit_exact():
         r0, r1 = torch.load(os.path.join(d, "r0.pt")), torch.load(os.path.join(d, "r1.pt"))
     for r in (r0, r1):
         for k, v in r.items():
-            if k.endswith("_ok") or k.endswith("_exact"):
+            if k.endswith("_ok") or k.endswith("_exact"):  # includes *_launches_ok
                 assert v, f"{k} failed: {r}"
     assert r1["nccl_bytes"] > 0

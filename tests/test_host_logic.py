@@ -241,3 +241,15 @@ def test_metrics_feed_the_gain_cost_file(tmp_path):
     assert merged == json.loads(path.read_text())
     assert merged["migration_cost"] == pytest.approx(0.003) and merged["preemption_penalty"] == 0.004
     assert merged["kv_transfer_bandwidth"] == pytest.approx(10000.0)
+
+
+def test_pull_and_push_orders_spread_the_first_flows():
+    sinks = [2, 3, 4, 5, 6, 7]
+    plan = MigrationPlan([Transfer(f"q{s}{d}", s, d, (1,), (1,)) for s in (0, 1) for d in sinks])
+    firsts = [plan.pull_order(d)[0] for d in sinks]
+    assert firsts.count(0) == 3 and firsts.count(1) == 3            # sources loaded evenly from the start
+    assert all(sorted(plan.pull_order(d)) == [0, 1] for d in sinks)
+    assert plan.push_order(0)[0] != plan.push_order(1)[0]            # sources start at different sinks
+    assert sorted(plan.push_order(0)) == sinks and plan.pull_order(0) == [] and plan.push_order(5) == []
+    lone = MigrationPlan([Transfer("a", 0, 1, (1,), (2,))])
+    assert lone.pull_order(1) == [0] and lone.push_order(0) == [1]
