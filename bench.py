@@ -252,8 +252,36 @@ class CpuPath:
                 "seconds": round(t_total, 2), "blocks_per_s": round(moved / t_total, 1)}
 
 
+    def run_c(self, budget_s):
+        """The same requests with the plain-C restatement (one memcpy per page, all host threads)."""
+        from oracle import kv_oracle_c
+
+        threads = os.cpu_count() or 1
+        w, nb = self.w, self.nb
+        gen = torch.Generator().manual_seed(1)
+        moved, t_total = 0, 0.0
+        for c in self.counts:
+            s = torch.randperm(nb, generator=gen)[:c].tolist()
+            d = torch.randperm(nb, generator=gen)[:c].tolist()
+            t0 = time.perf_counter()
+            kv_oracle_c.scatter(self.dst, d, kv_oracle_c.gather(self.src, s, threads=threads), threads=threads)
+            t_total += time.perf_counter() - t0
+            moved += c
+            if t_total > budget_s:
+                break
+        return {"value": round(moved * block_bytes(w) / t_total / 1e9, 3), "unit": "GB/s", "cores": threads,
+                "kind": "port", "what": "plain-C restatement, one memcpy per page on pthreads",
+                "seconds": round(t_total, 2)}
+
+
 def cpu_baseline(wname, budget_s=12.0):
-    return CpuPath(wname).run(budget_s)
+    path = CpuPath(wname)
+    out = path.run(budget_s)
+    try:
+        out["alt_c_memcpy"] = path.run_c(min(budget_s, 6.0))
+    except Exception as e:  # the C checker is optional for the baseline
+        out["alt_c_memcpy"] = {"error": f"{type(e).__name__}: {e}"}
+    return out
 
 
 def reference_arm(args):
@@ -350,6 +378,12 @@ def bench_single(args):
     peak, peak_kind = measured_peak()
     # gather reads and writes the payload once, scatter does the same: 4 x payload of HBM bytes per step
     achieved = 4 * payload * args.steps / (ms / 1e3) / 1e9
+    def step_direct():
+        for (s, d) in dev_tables:
+            src.copy_blocks(dst, s, d)
+
+    ms_direct = timed(step_direct, max(3, args.steps // 2), 3, device)
+    direct_steps = max(3, args.steps // 2)
     ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3, device)
     e2e_steps = max(3, args.steps // 4)
     e2e_value = payload * e2e_steps / (ms_e2e / 1e3) / 1e9
@@ -388,6 +422,11 @@ def bench_single(args):
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "cpu_baseline": cpu,
+        "variants": {"direct_block_copy": {
+            "value": round(payload * direct_steps / (ms_direct / 1e3) / 1e9, 2), "unit": "GB/s",
+            "hbm_gbs": round(2 * payload * direct_steps / (ms_direct / 1e3) / 1e9, 1),
+            "ms_per_step": round(ms_direct / direct_steps, 3),
+            "path": "pool A -> pool B in one launch per request, no packed buffer (the form used between GPUs)"}},
     }
     line.update(extras)
     print(json.dumps(line))

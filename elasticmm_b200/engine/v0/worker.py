@@ -26,6 +26,17 @@ from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_
                         pipelined_send, PIPELINE_DEPTH)
 from .utils import EngineStage
 
+import contextlib
+import os
+
+_NVTX = os.environ.get("EMM_NVTX", "0") == "1"
+
+
+def _range(name: str):
+    """NVTX range around a data-plane phase when EMM_NVTX=1 (for timeline tools); free otherwise."""
+    return torch.cuda.nvtx.range(name) if _NVTX else contextlib.nullcontext()
+
+
 _DTYPES = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
            "float32": torch.float32, "float": torch.float32}
 
@@ -126,13 +137,15 @@ class V0Worker:
     # -- gather / scatter (elasticmm/engine/v0/worker.py:578-647) --------------
     def extract_kv_blocks(self, block_indices: List[int]) -> torch.Tensor:
         """Returns [num_layers, 2, num_blocks, block_size, num_heads, head_size]."""
-        return self._require_pool().gather(block_indices)
+        with _range("emm.extract_kv_blocks"):
+            return self._require_pool().gather(block_indices)
 
     def write_kv_blocks(self, block_indices: List[int], kv_data: torch.Tensor) -> None:
         pool = self._require_pool()
         assert kv_data.shape[2] == len(block_indices), (
             f"Block count mismatch: {kv_data.shape[2]} vs {len(block_indices)}")
-        pool.scatter(block_indices, kv_data)
+        with _range("emm.write_kv_blocks"):
+            pool.scatter(block_indices, kv_data)
 
     def get_kv_cache_layout(self) -> Dict[str, Any]:
         if not self.kv_cache:
@@ -307,7 +320,7 @@ class V0Worker:
             slots = self._staging_views(pool, n, chunks)
             main = torch.cuda.current_stream(self.device)
             self._xfer_stream.wait_stream(main)
-            with torch.cuda.stream(self._xfer_stream):
+            with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_send_kv"):
                 pipelined_send(
                     chunks, self._buffer_for(pool, n, slots),
                     pack=lambda buf, b, c: pool.gather(ids, out=buf, layer_begin=b, layer_count=c),
@@ -336,7 +349,7 @@ class V0Worker:
             slots = self._staging_views(pool, n, chunks)
             main = torch.cuda.current_stream(self.device)
             self._xfer_stream.wait_stream(main)
-            with torch.cuda.stream(self._xfer_stream):
+            with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_recv_kv"):
                 pipelined_recv(
                     chunks, self._buffer_for(pool, n, slots),
                     irecv=lambda buf: dist.irecv(pool._logical(buf), src=src_rank, group=self.process_group),
@@ -448,7 +461,8 @@ class V0Worker:
             raise ValueError(f"Block count mismatch: src={len(src_blocks)}, dst={len(dst_blocks)}")
         pool = self._require_pool()
         try:
-            self.peer_pools[src_rank].copy_blocks(pool, src_blocks, dst_blocks, max_ctas=max_ctas)
+            with _range("emm.p2p_pull_kv"):
+                self.peer_pools[src_rank].copy_blocks(pool, src_blocks, dst_blocks, max_ctas=max_ctas)
         except _lib.EmmError as e:
             return {"error": str(e), "bytes": 0, "blocks": 0}
         return {"bytes": len(src_blocks) * pool.block_bytes(), "blocks": len(src_blocks)}

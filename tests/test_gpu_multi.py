@@ -158,3 +158,81 @@ def test_two_gpu_migration_is_bit_exact():
             if k.endswith("_ok") or k.endswith("_exact"):  # includes *_launches_ok
                 assert v, f"{k} failed: {r}"
     assert r1["nccl_bytes"] > 0
+
+
+def _plan4(seed):
+    """Two sources (ranks 0, 1) -> two sinks (ranks 2, 3), unequal request sizes."""
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer
+
+    g = torch.Generator().manual_seed(seed)
+    plan = MigrationPlan()
+    used = {2: 0, 3: 0}
+    dperm = {d: torch.randperm(GEOM["NB"], generator=g).tolist() for d in (2, 3)}
+    for s in (0, 1):
+        sperm = torch.randperm(GEOM["NB"], generator=g).tolist()
+        pos = 0
+        for r in range(6):
+            n = int(torch.randint(3, 60, (1,), generator=g))
+            d = 2 + int(torch.randint(0, 2, (1,), generator=g))
+            plan.add(Transfer(f"s{s}r{r}", s, d, tuple(sperm[pos:pos + n]), tuple(dperm[d][used[d]:used[d] + n])))
+            pos += n
+            used[d] += n
+    return plan
+
+
+def _worker4_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import TransferMethod, V0KVTransferManager, V0Worker
+    from oracle import kv_oracle
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    plan = _plan4(11)
+    plan.validate(lambda r: GEOM["NB"])
+    results = {}
+    for method in ("pull", "push", "nccl"):
+        is_src = rank < 2
+        cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16,
+                                  80 + rank if is_src else 0, fill="normal" if is_src else "guard")
+        w = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
+                     kv_cache=[t.to(dev) for t in cpu])
+        w.init_global_nccl()
+        if method != "nccl":
+            hs = [None] * world
+            dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
+            for peer in range(world):
+                if peer != rank:
+                    w.attach_peer_pool(peer, hs[peer][0], hs[peer][1])
+        if method == "pull":   # through the manager, as a role switch would call it
+            mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
+            mgr.register_worker(rank, w, "prefill" if is_src else "decoding")
+            results[f"{method}_ok"] = mgr.transfer_many(plan)
+        else:
+            results[f"{method}_ok"] = "error" not in w.migrate(plan, method=method)
+        dist.barrier()
+        if not is_src:
+            want = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0,
+                                       fill="guard")
+            for s in plan.incoming(rank):
+                si, di = plan.tables(s, rank)
+                src_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"],
+                                              torch.bfloat16, 80 + s)
+                kv_oracle.write_kv_blocks(want, di, kv_oracle.extract_kv_blocks(src_cpu, si))
+            results[f"{method}_exact"] = all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, want))
+        dist.barrier()
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_four_gpu_two_sources_two_sinks_is_bit_exact():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker4_main, args=(4, _free_port(), d), nprocs=4, join=True)
+        for r in range(4):
+            res = torch.load(os.path.join(d, f"r{r}.pt"))
+            assert res and all(res.values()), f"rank {r}: {res}"
