@@ -406,6 +406,44 @@ class V0Worker:
         return {"bytes": result["bytes"], "blocks": len(dst_blocks), "elapsed": elapsed,
                 "method": "coordinated_single_call"}
 
+    def collective_transfer_kv(self, group_name: Any, root: int, block_indices: List[int],
+                               tensor_shape: Sequence[int], dtype: str, mode: str) -> Dict[str, Any]:
+        """Broadcast form of the transfer (elasticmm/engine/v0/worker.py:939-1005): the
+        sender gathers its blocks into one flat message and broadcasts it from `root`; a
+        receiver takes the broadcast and scatters it into `block_indices`. `group_name` is a
+        torch.distributed process group (or None for the default group) where the reference
+        passes the name of a Ray collective group.
+        """
+        key = dtype.replace("torch.", "").lower()
+        names = {"float16": torch.float16, "half": torch.float16, "fp16": torch.float16,
+                 "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+                 "fp32": torch.float32}
+        if key not in names:
+            raise ValueError(f"[V0Worker] Unsupported dtype for collective transfer: {dtype}")
+        group = None if isinstance(group_name, str) else group_name
+        shape = tuple(int(d) for d in tensor_shape)
+        if mode == "send":
+            flat = self.extract_kv_blocks(block_indices).contiguous().view(-1).to(dtype=names[key])
+            dist.broadcast(flat, src=root, group=group)
+        elif mode == "recv":
+            numel = 1
+            for d in shape:
+                numel *= d
+            flat = torch.empty(numel, dtype=names[key], device=self.device)
+            dist.broadcast(flat, src=root, group=group)
+            self.write_kv_blocks(block_indices, flat.view(shape))
+        else:
+            raise ValueError(f"[V0Worker] Unknown collective transfer mode: {mode}")
+        torch.cuda.synchronize(self.device)
+        return {"bytes": flat.numel() * flat.element_size(), "mode": mode}
+
+    def get_kv_cache_shape(self) -> tuple:
+        """Shape of one layer's pool tensor (the reference calls `.shape` on its list of
+        layers, which raises; this returns the per-layer shape with the layer count first)."""
+        if not self.kv_cache:
+            return ()
+        return (len(self.kv_cache),) + tuple(self.kv_cache[0].shape)
+
     # -- direct peer stores (the slot the reference reserves for a CUDA-IPC
     #    extension, elasticmm/engine/v0/kv_transfer.py:303-331) ----------------
     def get_ipc_handles(self) -> List[Tuple[bytes, int]]:

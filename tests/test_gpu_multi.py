@@ -121,6 +121,17 @@ def _worker_main(rank, world, port, out_dir):
             results[f"plan_{method}_exact"] = same(w2, expect(reqs))
         dist.barrier()
 
+    # 3b. broadcast form (the reference's collective_transfer_kv)
+    wb, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    rid, s_ids, d_ids = reqs[0]
+    shape = (GEOM["L"], 2, len(s_ids), GEOM["BS"], GEOM["H"], GEOM["D"])
+    res = wb.collective_transfer_kv(None, 0, s_ids if rank == 0 else d_ids, shape, "torch.bfloat16",
+                                    "send" if rank == 0 else "recv")
+    results["broadcast_ok"] = res["bytes"] == 2 * len(s_ids) * GEOM["L"] * GEOM["BS"] * GEOM["H"] * GEOM["D"] * 2
+    if rank == 1:
+        results["broadcast_exact"] = same(wb, expect(reqs[:1]))
+    dist.barrier()
+
     # 4. exchange: both ranks are source and sink at once (peer method only)
     w3, _ = fresh(70, guard=False)
     sink_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0,
