@@ -481,6 +481,19 @@ def bench_append(ctx, device, args):
     ms = timed(per_layer, steps, 5, device)
     out["per_layer_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
                               "launches_per_step": L}
+    slot_buf = maps[0].clone()
+    bound = pool.bind_append(key, value, slot_buf)
+
+    def per_layer_bound():
+        slot_buf.copy_(maps[it["i"] % 16])
+        it["i"] += 1
+        for l in range(L):
+            bound(l)
+
+    ms = timed(per_layer_bound, steps, 5, device)
+    out["per_layer_bound_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)),
+                                    "us_per_step": round(ms * 1e3 / steps, 2), "launches_per_step": L,
+                                    "what": "static key/value/slot buffers validated once (KVPool.bind_append)"}
     # CUDA-graph replay of the per-layer sequence (how a captured decode step issues it)
     try:
         stream = torch.cuda.Stream(device)

@@ -404,6 +404,35 @@ class KVPool:
         if rc:
             _lib.check(rc)
 
+    def bind_append(self, key: torch.Tensor, value: torch.Tensor, slot_mapping: torch.Tensor):
+        """Pre-validated per-layer append over static buffers.
+
+        `key` / `value` are [L, T, H, D] buffers and `slot_mapping` a [T] int64
+        buffer that the caller refills in place every step (the usual shape of
+        a graph-captured decode step). Returns `append(layer)`, which launches
+        reshape_and_cache for that layer on the current stream at the cost of
+        one foreign call.
+        """
+        T = self._check_kv(key, value, slot_mapping, 1)
+        if key.shape[0] != self.num_layers:
+            raise ValueError(f"key has {key.shape[0]} layers, pool has {self.num_layers}")
+        e = self.elem_size
+        fn, h = self._emm_append, self._h
+        kp, vp, sp = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
+        kls, vls = key.stride(0) * e, value.stride(0) * e
+        kts, vts = key.stride(1) * e, value.stride(1) * e
+        device = self.ctx.device
+        keep = (key, value, slot_mapping)  # the closure keeps the buffers alive
+
+        def append(layer: int) -> None:
+            rc = fn(h, layer, kp + layer * kls, vp + layer * vls, kts, vts, sp, T,
+                    torch.cuda.current_stream(device).cuda_stream)
+            if rc:
+                _lib.check(rc)
+
+        append.buffers = keep
+        return append
+
     def append_all_layers(self, key: torch.Tensor, value: torch.Tensor,
                           slot_mapping: torch.Tensor) -> None:
         """reshape_and_cache for every layer in one launch; key/value are [L, T, H, D]."""

@@ -47,9 +47,14 @@ def test_append_per_layer_and_all_layers(ctx, geom):
     assert ctx.launch_count - before == L
     pool2.append_all_layers(key_d, value_d, slots_d)
     assert ctx.launch_count - before == L + 1
+    pool3 = KVPool(to_gpu(pool_cpu2), ctx)          # static-buffer form: validated once, one call per layer
+    bound = pool3.bind_append(key_d, value_d, slots_d)
+    for l in range(L):
+        bound(l)
     assert_clean(ctx)
     assert pools_equal(pool.layers, pool_cpu)
     assert pools_equal(pool2.layers, pool_cpu)
+    assert pools_equal(pool3.layers, pool_cpu)
 
 
 def test_append_strided_key_value_and_head_major_pool(ctx):
