@@ -4,17 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One "step" migrates every request of the workload once.
-  N = 1   BASELINE config 1 geometry (Llama-7B-shaped pool, fp16): each request is
+  N = 1   Llama-7B-shaped pool (32 layers, 32 KV heads, fp16, 2048 blocks), 64 requests: each request is
           gathered from pool A into a contiguous buffer and scattered into pool B
           under an independent block table, in waves that fit the 2048-block pool.
-  N = 2   BASELINE config 3 (Qwen2.5-VL-7B-shaped pool, bf16): rank 0 -> rank 1 (the sink pulls).
-  N = 4   BASELINE config 4 subset (LLaVA-13B-shaped pool, fp16): 2 sources -> 2 sinks.
-  N = 8   BASELINE config 4: 2 sources -> 6 sinks, in waves bounded by the pools.
+  N = 2   Qwen2.5-VL-7B-shaped pool (28 layers, 4 KV heads, bf16), 128 requests with a 576-token image
+          prefix: rank 0 -> rank 1 (the sink pulls).
+  N = 4   LLaVA-13B-shaped pool (40 layers, 40 KV heads, fp16), 512 requests: 2 sources -> 2 sinks.
+  N = 8   the same 512 requests: 2 sources -> 6 sinks, in waves bounded by the pools.
 For N > 1 launch under torchrun (one rank per GPU). The line's `value` is the
 whole-job payload rate with tables resident on the device; `e2e` is the same
 workload through the engine/v0 worker API with host block-id lists, table upload
-and a device->host status read inside the timed region. Append (config 2) and
-compaction (config 5) are reported as extra objects at N = 1.
+and a device->host status read inside the timed region. Decode-time append (256 tokens
+x 32 layers, 8 KV heads) and eviction + compaction (70B-shaped GQA pool) are reported as
+extra objects at N = 1.
 
 All data is synthetic: seeded N(0,1) values with the named shapes; no model
 weights or datasets are involved. `--impl reference` times the CPU restatement
@@ -439,7 +441,7 @@ TRAFFIC_RATIO = {"page_copy": (880.883456 + 832.828416) / (2 * 880.80384)}
 
 
 def bench_append(ctx, device, args):
-    """Config 2: reshape_and_cache of [256, 8, 128] bf16 per layer into a 32-layer, 16384-block pool."""
+    """Decode-time append: reshape_and_cache of [256, 8, 128] bf16 per layer into a 32-layer, 16384-block pool."""
     from elasticmm_b200 import KVPool
 
     w = WORKLOADS["append_cfg2"]
@@ -515,7 +517,7 @@ def bench_append(ctx, device, args):
 
 
 def bench_compaction(ctx, device, args):
-    """Config 5: evict 30 % of the requests of an 85 %-full 8192-block pool, compact the survivors."""
+    """Eviction + defragmentation: evict 30 % of the requests of an 85 %-full 8192-block pool, compact the survivors."""
     from elasticmm_b200 import KVPool, compact_plan
 
     w = WORKLOADS["gqa70b_cfg5"]

@@ -19,7 +19,9 @@ from typing import List, Optional, Sequence
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("ELASTICMM_REFERENCE_ROOT", "/root/reference")
+# The reference checkout sits beside this repository unless ELASTICMM_REFERENCE_ROOT says otherwise.
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_ROOT = os.environ.get("ELASTICMM_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 
 
 def reference_available() -> bool:

@@ -1,4 +1,4 @@
-"""BASELINE geometries at full size on one B200, checked through size-independent
+"""The benchmark geometries at full size on one B200, checked through size-independent
 properties (round trips, untouched-guard counts, per-block checksums) plus the
 CPU oracle on whole layers copied back to the host."""
 import pytest
