@@ -326,7 +326,7 @@ def bench_single(args):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     ctx = get_context(0)
-    wname = "llama7b_cfg1"
+    wname = args.workload
     w = WORKLOADS[wname]
     src_worker = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 1))
     dst_worker = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 0, guard=True))
@@ -401,6 +401,7 @@ def bench_single(args):
         extras["compaction"] = bench_compaction(ctx, device, args)
         torch.cuda.empty_cache()
     cpu = cpu_baseline(wname) if not args.skip_cpu else None
+    kernel_name = "page_copy_ldg" if ctx.get_option(_lib.OPT_COPY_VARIANT) == _lib.COPY_LDG else "page_copy_bulk"
 
     line = {
         "metric": "kv_migration_payload_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": 1,
@@ -416,7 +417,7 @@ def bench_single(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": round(TRAFFIC_RATIO["page_copy"] * 2 * payload / len(reqs)),
                      "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": round(achieved / 8000.0, 4),
-                     "kernel": "page_copy_bulk", "algorithmic_bytes_per_launch":
+                     "kernel": kernel_name, "algorithmic_bytes_per_launch":
                          round(2 * payload / len(reqs)), "avg_launch_us": round(ms * 1e3 / launches, 2)},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16,
                 "api": "V0Worker.extract_kv_blocks + write_kv_blocks per request, host id lists",
@@ -883,6 +884,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true",
                     help="N=1: the same geometries on pools of a few GiB and 8 requests (the case profiled under ncu)")
+    ap.add_argument("--workload", default="llama7b_cfg1",
+                    choices=["llama7b_cfg1", "qwen25vl7b_cfg3", "llava13b_cfg4"],
+                    help="N=1: pool geometry and request mix of the gather -> scatter step (default: the headline one)")
     ap.add_argument("--skip-extras", action="store_true", help="N=1: skip the append and compaction objects")
     ap.add_argument("--skip-cpu", action="store_true", help="N=1: skip the CPU baseline leg")
     ap.add_argument("--probe-fabric", action="store_true",
@@ -897,6 +901,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.small:
         WORKLOADS["llama7b_cfg1"].update(NB=256, requests=8)
+        WORKLOADS["qwen25vl7b_cfg3"].update(NB=4096, requests=16)
+        WORKLOADS["llava13b_cfg4"].update(NB=256, requests=8, tokens=("loguniform", 256, 2048))
         WORKLOADS["append_cfg2"].update(NB=1024)
         WORKLOADS["gqa70b_cfg5"].update(NB=512, tokens=("uniform", 512, 2048))
     if args.impl == "reference":
