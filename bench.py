@@ -279,6 +279,15 @@ class CpuPath:
 def cpu_baseline(wname, budget_s=12.0):
     path = CpuPath(wname)
     out = path.run(budget_s)
+    threads = torch.get_num_threads()
+    try:  # the same path on one thread (a few seconds)
+        torch.set_num_threads(1)
+        path.threads = 1
+        one = path.run(min(budget_s, 3.0))
+        out["single_thread"] = {"value": one["value"], "unit": "GB/s", "cores": 1, "seconds": one["seconds"]}
+    finally:
+        torch.set_num_threads(threads)
+        path.threads = threads
     try:
         out["alt_c_memcpy"] = path.run_c(min(budget_s, 6.0))
     except Exception as e:  # the C checker is optional for the baseline
@@ -386,12 +395,25 @@ def bench_single(args):
 
     ms_direct = timed(step_direct, max(3, args.steps // 2), 3, device)
     direct_steps = max(3, args.steps // 2)
+    # the same copies batched: one launch per wave over the concatenated tables (what a plan-level call issues)
+    wave_tables, pos = [], 0
+    for wave in waves:
+        s_cat = torch.cat([dev_tables[pos + k][0] for k in range(len(wave))])
+        d_cat = torch.cat([dev_tables[pos + k][1] for k in range(len(wave))])
+        wave_tables.append((s_cat, d_cat))
+        pos += len(wave)
+
+    def step_direct_waves():
+        for (s, d) in wave_tables:
+            src.copy_blocks(dst, s, d)
+
+    ms_dw = timed(step_direct_waves, direct_steps, 3, device)
     ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3, device)
     e2e_steps = max(3, args.steps // 4)
     e2e_value = payload * e2e_steps / (ms_e2e / 1e3) / 1e9
     h2d = sum(4 * (len(s) + len(d)) for s, d in reqs)
 
-    del packed, flat, dev_tables
+    del packed, flat, dev_tables, wave_tables
     extras = {}
     if not args.skip_extras:
         src_worker = dst_worker = src = dst = None
@@ -429,7 +451,12 @@ def bench_single(args):
             "value": round(payload * direct_steps / (ms_direct / 1e3) / 1e9, 2), "unit": "GB/s",
             "hbm_gbs": round(2 * payload * direct_steps / (ms_direct / 1e3) / 1e9, 1),
             "ms_per_step": round(ms_direct / direct_steps, 3),
-            "path": "pool A -> pool B in one launch per request, no packed buffer (the form used between GPUs)"}},
+            "path": "pool A -> pool B in one launch per request, no packed buffer (the form used between GPUs)"},
+            "direct_block_copy_per_wave": {
+                "value": round(payload * direct_steps / (ms_dw / 1e3) / 1e9, 2), "unit": "GB/s",
+                "hbm_gbs": round(2 * payload * direct_steps / (ms_dw / 1e3) / 1e9, 1),
+                "ms_per_step": round(ms_dw / direct_steps, 3), "launches_per_step": len(waves),
+                "path": "the same copies with one launch per wave over concatenated tables (plan-level batching)"}},
     }
     line.update(extras)
     print(json.dumps(line))
@@ -769,6 +796,9 @@ def bench_multi(args):
                                "side on separate streams with grids capped to one CTA per SM in total: NVLink loads "
                                "from the source's peer-mapped pool, local stores", "l2": "inputs larger than L2",
                        "per_source_egress_gbs": round(per_src_gbs, 2),
+                       "per_sink_ingress_gbs": round(value / len(sinks), 2),
+                       "per_pair_mean_gbs": round(value / (len(sources) * len(sinks)), 2),
+                       "per_sink_ingress_frac_of_900": round(value / len(sinks) / 900.0, 4),
                        "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
             "verified_bit_exact_checksum": verified,
             "roofline": {"bound": "nvlink", "achieved": round(per_src_gbs, 1), "peak": NVLINK_PEER_COPY_GBS,
