@@ -58,6 +58,11 @@ class V0KVTransferManager:
         self.total_transfer_time = 0.0
         self.total_bytes_transferred = 0
         self.first_transfer_done = False
+        # batching: small transfers of one (source, sink) pair are merged into one table
+        self._transfer_queue: Dict[tuple, List[tuple]] = {}
+        self._last_flush_time: Dict[tuple, float] = {}
+        self._batch_flush_threshold = batch_size
+        self._batch_flush_timeout = batch_timeout
 
     # -- registry --------------------------------------------------------------
     @staticmethod
@@ -152,8 +157,45 @@ class V0KVTransferManager:
         """True if the request's blocks were moved (same contract as the reference)."""
         return self.transfer_kv_cache_sync(request_id, src_rank, dst_rank, src_blocks, dst_blocks)
 
+    def flush(self, src_rank: Optional[int] = None, dst_rank: Optional[int] = None) -> bool:
+        """Moves what is queued for a pair (or for every pair) as one merged transfer per pair."""
+        ok = True
+        for key in [k for k in self._transfer_queue if (src_rank is None or k[0] == src_rank)
+                    and (dst_rank is None or k[1] == dst_rank)]:
+            queued = self._transfer_queue.pop(key, [])
+            self._last_flush_time[key] = time.perf_counter()
+            if not queued:
+                continue
+            src_all = [b for _, s, _ in queued for b in s]
+            dst_all = [b for _, _, d in queued for b in d]
+            start = time.perf_counter()
+            try:
+                res = self._run(key[0], key[1], src_all, dst_all)
+            except Exception as e:
+                res = {"error": f"{type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+            self.last_result = res
+            if "error" in res or (res.get("bytes", 0) == 0 and not res.get("passive")):
+                ok = False
+                continue
+            self._account(time.perf_counter() - start, res.get("bytes", 0), len(src_all), count=len(queued))
+        return ok
+
     def transfer_kv_cache_sync(self, request_id: str, src_rank: int, dst_rank: int,
                                src_blocks: List[int], dst_blocks: List[int]) -> bool:
+        if self.enable_batching and self.transfer_method != TransferMethod.P2P_COPY:
+            # Merge small transfers of the same pair (the intent of the reference's batching branch,
+            # elasticmm/engine/v0/kv_transfer.py:342-418,437-465): queue, and flush once `batch_size`
+            # requests wait or `batch_timeout` has passed since the pair's last flush.
+            if len(src_blocks) != len(dst_blocks):
+                return False
+            key = (src_rank, dst_rank)
+            now = time.perf_counter()
+            self._transfer_queue.setdefault(key, []).append((request_id, list(src_blocks), list(dst_blocks)))
+            self._last_flush_time.setdefault(key, now)
+            if (len(self._transfer_queue[key]) >= self._batch_flush_threshold
+                    or now - self._last_flush_time[key] >= self._batch_flush_timeout):
+                return self.flush(src_rank, dst_rank)
+            return True  # queued; moved by a later call or by flush()
         start = time.perf_counter()
         try:
             res = self._run(src_rank, dst_rank, list(src_blocks), list(dst_blocks))

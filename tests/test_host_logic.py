@@ -253,3 +253,41 @@ def test_pull_and_push_orders_spread_the_first_flows():
     assert sorted(plan.push_order(0)) == sinks and plan.pull_order(0) == [] and plan.push_order(5) == []
     lone = MigrationPlan([Transfer("a", 0, 1, (1,), (2,))])
     assert lone.pull_order(1) == [0] and lone.push_order(0) == [1]
+
+
+def test_manager_batching_merges_a_pair_into_one_transfer():
+    """enable_batching: requests of one (source, sink) pair are queued and moved as one merged table."""
+
+    class Recorder:
+        def __init__(self):
+            self.calls = []
+            self.peer_pools = {0: object()}
+            self.device = None
+
+        def p2p_pull_kv(self, src_rank, src_blocks, dst_blocks):
+            self.calls.append((src_rank, list(src_blocks), list(dst_blocks)))
+            return {"bytes": 100 * len(src_blocks), "blocks": len(src_blocks)}
+
+    sink = Recorder()
+    seen = []
+    mgr = V0KVTransferManager(TransferMethod.B200_PEER, enable_batching=True, batch_size=3, batch_timeout=3600.0,
+                              metrics_callback=lambda transfer_time_sec, num_blocks: seen.append(num_blocks))
+    mgr.register_worker(1, sink, "decoding")
+    import torch
+
+    real_sync = torch.cuda.synchronize
+    torch.cuda.synchronize = lambda *a, **k: None
+    sink.ctx = type("C", (), {"status": staticmethod(lambda: (0, 0))})()
+    try:
+        assert mgr.transfer_kv_cache_sync("a", 0, 1, [1, 2], [7, 8]) and sink.calls == []
+        assert mgr.transfer_kv_cache_sync("b", 0, 1, [3], [9]) and sink.calls == []
+        assert mgr.transfer_kv_cache_sync("c", 0, 1, [4, 5], [0, 1])                 # third request: flush
+        assert sink.calls == [(0, [1, 2, 3, 4, 5], [7, 8, 9, 0, 1])]
+        assert mgr.transfer_kv_cache_sync("d", 0, 1, [6], [2]) and len(sink.calls) == 1  # queued again
+        assert not mgr.transfer_kv_cache_sync("bad", 0, 1, [6, 7], [2])               # count mismatch refused
+        assert mgr.flush() and sink.calls[-1] == (0, [6], [2])
+        assert mgr.flush() and len(sink.calls) == 2                                    # nothing left
+    finally:
+        torch.cuda.synchronize = real_sync
+    assert seen == [5, 1]                       # one metrics sample per merged transfer
+    assert mgr.get_stats()["transfer_count"] == 1   # the first (cold) merged transfer is not averaged
