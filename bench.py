@@ -752,6 +752,16 @@ def bench_multi(args):
     except Exception as e:
         variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
 
+    try:  # the same staged pipeline run inside the C library on its own communicator and streams
+        worker.init_native_nccl()
+        ms_nn = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
+        variants["nccl_staged_native"] = {"value": round(payload * nccl_steps / (ms_nn / 1e3) / 1e9, 2), "unit": "GB/s",
+                                          "ms_per_step": round(ms_nn / nccl_steps, 3),
+                                          "path": "emm_send_blocks / emm_recv_blocks: pack -> ncclSend, ncclRecv -> "
+                                                  "unpack on library streams"}
+    except Exception as e:
+        variants["nccl_staged_native"] = {"error": f"{type(e).__name__}: {e}"}
+
     # Every rank a source and a sink at once (the rebalancing exchange): rank r loads the lower half of
     # rank r+1's pool into the upper half of its own. Run last among the device-resident variants because
     # it overwrites pool contents.

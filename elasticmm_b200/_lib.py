@@ -15,6 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libemm_kv.so"
 IPC_HANDLE_BYTES = 64
 NOALLOC_MAX_IDS = 16384
 NOALLOC_MAX_LAYERS = 256
+NCCL_UNIQUE_ID_BYTES = 128
 
 # enum emm_status
 OK = 0
@@ -28,6 +29,7 @@ ERR_DUPLICATE = 7
 ERR_OVERLAP = 8
 ERR_TOO_LARGE = 9
 ERR_NOMEM = 10
+ERR_NCCL = 11
 
 # enum emm_copy_variant
 COPY_AUTO, COPY_BULK, COPY_LDG = 0, 1, 2
@@ -109,6 +111,14 @@ SIGNATURES = {
         [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, _P, C.c_int32, _P],
     ),
     "emm_compact_plan": (C.c_int, [_I64P, C.c_int64, C.c_int64, _I64P, _I64P, _I64P, _I64P]),
+    "emm_nccl_unique_id": (C.c_int, [C.c_char_p]),
+    "emm_nccl_comm_init": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.POINTER(_P)]),
+    "emm_nccl_comm_destroy": (C.c_int, [_P]),
+    "emm_send_packed": (C.c_int, [_P, _P, C.c_uint64, C.c_int, _P]),
+    "emm_recv_packed": (C.c_int, [_P, _P, C.c_uint64, C.c_int, _P]),
+    "emm_exchange": (C.c_int, [_P, C.c_int32, _I32P, C.POINTER(_P), C.POINTER(C.c_uint64), _I32P, _P]),
+    "emm_send_blocks": (C.c_int, [_P, _P, C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_int32, _P]),
+    "emm_recv_blocks": (C.c_int, [_P, _P, C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_int32, _P]),
     "emm_ipc_export": (C.c_int, [_P, _P, C.c_char_p, C.POINTER(C.c_uint64)]),
     "emm_ipc_open": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.POINTER(_P)]),
 }

@@ -4,6 +4,7 @@
 #include "emm_kv.h"
 
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <cstdarg>
@@ -101,6 +102,13 @@ struct emm_ctx {
   int next_slot = 0;
   std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
   std::vector<IpcMapping> ipc;
+  // staged transport: a packing/unpacking stream, a wire stream and their events (made on first use)
+  cudaStream_t copy_stream = nullptr;
+  cudaStream_t wire_stream = nullptr;
+  cudaEvent_t ev_entry = nullptr;
+  cudaEvent_t ev_copied[2] = {nullptr, nullptr};
+  cudaEvent_t ev_wired[2] = {nullptr, nullptr};
+  cudaEvent_t ev_done[2] = {nullptr, nullptr};
 };
 
 struct emm_pool {
@@ -408,6 +416,7 @@ const char *emm_status_string(int status) {
     case EMM_ERR_OVERLAP: return "source and destination ids overlap";
     case EMM_ERR_TOO_LARGE: return "size exceeds capacity";
     case EMM_ERR_NOMEM: return "out of memory";
+    case EMM_ERR_NCCL: return "NCCL unavailable or failed";
     default: return "unknown status";
   }
 }
@@ -451,6 +460,11 @@ int emm_ctx_destroy(emm_ctx *ctx) {
     if (s.ev) cudaEventDestroy(s.ev);
   }
   for (IpcMapping &m : ctx->ipc) cudaIpcCloseMemHandle(m.base);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  if (ctx->wire_stream) cudaStreamDestroy(ctx->wire_stream);
+  for (cudaEvent_t e : {ctx->ev_entry, ctx->ev_copied[0], ctx->ev_copied[1], ctx->ev_wired[0], ctx->ev_wired[1],
+                        ctx->ev_done[0], ctx->ev_done[1]})
+    if (e) cudaEventDestroy(e);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   delete ctx;
@@ -953,6 +967,246 @@ int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES],
   return EMM_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Staged transport over NCCL (entry points resolved with dlopen / dlsym)
+// ---------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+struct NcclUniqueId {
+  char internal[EMM_NCCL_UNIQUE_ID_BYTES];
+};
+typedef int (*nccl_get_unique_id_fn)(NcclUniqueId *);
+typedef int (*nccl_comm_init_rank_fn)(void **, int, NcclUniqueId, int);
+typedef int (*nccl_comm_destroy_fn)(void *);
+typedef int (*nccl_send_fn)(const void *, size_t, int, int, void *, cudaStream_t);
+typedef int (*nccl_recv_fn)(void *, size_t, int, int, void *, cudaStream_t);
+typedef int (*nccl_group_fn)(void);
+typedef const char *(*nccl_error_string_fn)(int);
+constexpr int kNcclInt8 = 0;  // ncclInt8 / ncclChar
+
+struct NcclApi {
+  bool tried = false;
+  void *lib = nullptr;
+  nccl_get_unique_id_fn get_unique_id = nullptr;
+  nccl_comm_init_rank_fn comm_init_rank = nullptr;
+  nccl_comm_destroy_fn comm_destroy = nullptr;
+  nccl_send_fn send = nullptr;
+  nccl_recv_fn recv = nullptr;
+  nccl_group_fn group_start = nullptr;
+  nccl_group_fn group_end = nullptr;
+  nccl_error_string_fn error_string = nullptr;
+};
+NcclApi g_nccl;
+
+int nccl_api(NcclApi **out) {
+  NcclApi &a = g_nccl;
+  if (!a.tried) {
+    a.tried = true;
+    const char *override_path = getenv("EMM_NCCL_LIB");
+    // Prefer the copy the process has already loaded (the host framework's), then the search path.
+    if (override_path && *override_path) a.lib = dlopen(override_path, RTLD_NOW | RTLD_GLOBAL);
+    if (!a.lib) a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!a.lib) a.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (a.lib) {
+      a.get_unique_id = (nccl_get_unique_id_fn)dlsym(a.lib, "ncclGetUniqueId");
+      a.comm_init_rank = (nccl_comm_init_rank_fn)dlsym(a.lib, "ncclCommInitRank");
+      a.comm_destroy = (nccl_comm_destroy_fn)dlsym(a.lib, "ncclCommDestroy");
+      a.send = (nccl_send_fn)dlsym(a.lib, "ncclSend");
+      a.recv = (nccl_recv_fn)dlsym(a.lib, "ncclRecv");
+      a.group_start = (nccl_group_fn)dlsym(a.lib, "ncclGroupStart");
+      a.group_end = (nccl_group_fn)dlsym(a.lib, "ncclGroupEnd");
+      a.error_string = (nccl_error_string_fn)dlsym(a.lib, "ncclGetErrorString");
+    }
+  }
+  if (!a.lib || !a.get_unique_id || !a.comm_init_rank || !a.comm_destroy || !a.send || !a.recv ||
+      !a.group_start || !a.group_end)
+    return fail(EMM_ERR_NCCL, "libnccl.so.2 could not be loaded (set EMM_NCCL_LIB to its path): %s",
+                a.lib ? "a symbol is missing" : "not found");
+  *out = &a;
+  return EMM_OK;
+}
+
+int nccl_fail(NcclApi *a, const char *what, int rc) {
+  return fail(EMM_ERR_NCCL, "%s failed: %s (%d)", what, a->error_string ? a->error_string(rc) : "?", rc);
+}
+
+#define EMM_NCCL(api, call)                          \
+  do {                                               \
+    int r_ = (call);                                 \
+    if (r_ != 0) return nccl_fail((api), #call, r_); \
+  } while (0)
+
+int transport_setup(emm_ctx *ctx) {
+  if (ctx->copy_stream) return EMM_OK;
+  EMM_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+  EMM_CUDA(cudaStreamCreateWithFlags(&ctx->wire_stream, cudaStreamNonBlocking));
+  cudaEvent_t *evs[] = {&ctx->ev_entry,    &ctx->ev_copied[0], &ctx->ev_copied[1], &ctx->ev_wired[0],
+                        &ctx->ev_wired[1], &ctx->ev_done[0],   &ctx->ev_done[1]};
+  for (cudaEvent_t *e : evs) EMM_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+  return EMM_OK;
+}
+
+int check_blocks_args(emm_pool *pool, void *comm, const int32_t *d_ids, int32_t n, void *d_staging,
+                      uint64_t staging_bytes, int32_t layers_per_msg, const char *what) {
+  if (int rc = check_pool_for_pages(pool, what)) return rc;
+  if (!comm) return fail(EMM_ERR_BAD_ARG, "%s: null communicator", what);
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "%s: negative block count", what);
+  if (n == 0) return EMM_OK;
+  if (!d_ids || !d_staging) return fail(EMM_ERR_BAD_ARG, "%s: null pointer", what);
+  if (layers_per_msg < 1 || layers_per_msg > pool->desc.num_layers)
+    return fail(EMM_ERR_BAD_ARG, "%s: layers_per_msg %d outside [1, %d]", what, layers_per_msg,
+                pool->desc.num_layers);
+  const uint64_t msg = (uint64_t)layers_per_msg * pool->planes * (uint64_t)n * (uint64_t)pool->page_bytes;
+  if (staging_bytes < 2 * msg)
+    return fail(EMM_ERR_LENGTH, "%s: staging buffer holds %llu bytes, two messages need %llu", what,
+                (unsigned long long)staging_bytes, (unsigned long long)(2 * msg));
+  return EMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int emm_nccl_unique_id(unsigned char id[EMM_NCCL_UNIQUE_ID_BYTES]) {
+  if (!id) return fail(EMM_ERR_BAD_ARG, "nccl_unique_id: null output");
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  NcclUniqueId u;
+  EMM_NCCL(api, api->get_unique_id(&u));
+  memcpy(id, u.internal, EMM_NCCL_UNIQUE_ID_BYTES);
+  return EMM_OK;
+}
+
+int emm_nccl_comm_init(emm_ctx *ctx, const unsigned char id[EMM_NCCL_UNIQUE_ID_BYTES], int nranks,
+                       int rank, void **comm) {
+  if (!ctx || !id || !comm) return fail(EMM_ERR_BAD_ARG, "nccl_comm_init: null argument");
+  if (nranks < 1 || rank < 0 || rank >= nranks)
+    return fail(EMM_ERR_BAD_ARG, "nccl_comm_init: rank %d of %d", rank, nranks);
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  NcclUniqueId u;
+  memcpy(u.internal, id, EMM_NCCL_UNIQUE_ID_BYTES);
+  *comm = nullptr;
+  EMM_NCCL(api, api->comm_init_rank(comm, nranks, u, rank));
+  return EMM_OK;
+}
+
+int emm_nccl_comm_destroy(void *comm) {
+  if (!comm) return EMM_OK;
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  EMM_NCCL(api, api->comm_destroy(comm));
+  return EMM_OK;
+}
+
+int emm_send_packed(void *comm, const void *d_buf, uint64_t bytes, int peer, void *stream) {
+  if (!comm || (!d_buf && bytes)) return fail(EMM_ERR_BAD_ARG, "send_packed: null argument");
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  if (bytes == 0) return EMM_OK;
+  EMM_NCCL(api, api->send(d_buf, (size_t)bytes, kNcclInt8, peer, comm, (cudaStream_t)stream));
+  return EMM_OK;
+}
+
+int emm_recv_packed(void *comm, void *d_buf, uint64_t bytes, int peer, void *stream) {
+  if (!comm || (!d_buf && bytes)) return fail(EMM_ERR_BAD_ARG, "recv_packed: null argument");
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  if (bytes == 0) return EMM_OK;
+  EMM_NCCL(api, api->recv(d_buf, (size_t)bytes, kNcclInt8, peer, comm, (cudaStream_t)stream));
+  return EMM_OK;
+}
+
+int emm_exchange(void *comm, int32_t n_ops, const int32_t *is_send, void *const *bufs,
+                 const uint64_t *bytes, const int32_t *peers, void *stream) {
+  if (!comm || n_ops < 0) return fail(EMM_ERR_BAD_ARG, "exchange: bad argument");
+  if (n_ops == 0) return EMM_OK;
+  if (!is_send || !bufs || !bytes || !peers) return fail(EMM_ERR_BAD_ARG, "exchange: null array");
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  EMM_NCCL(api, api->group_start());
+  int first_error = 0;
+  for (int32_t k = 0; k < n_ops && !first_error; ++k) {
+    if (bytes[k] == 0) continue;
+    first_error = is_send[k] ? api->send(bufs[k], (size_t)bytes[k], kNcclInt8, peers[k], comm, (cudaStream_t)stream)
+                             : api->recv(bufs[k], (size_t)bytes[k], kNcclInt8, peers[k], comm, (cudaStream_t)stream);
+  }
+  const int end_rc = api->group_end();  // always close the group
+  if (first_error) return nccl_fail(api, "ncclSend/ncclRecv inside the group", first_error);
+  if (end_rc) return nccl_fail(api, "ncclGroupEnd", end_rc);
+  return EMM_OK;
+}
+
+// Shared body of emm_send_blocks / emm_recv_blocks.
+static int staged_blocks(emm_pool *pool, void *comm, int peer, const int32_t *d_ids, int32_t n,
+                         void *d_staging, uint64_t staging_bytes, int32_t layers_per_msg, void *stream,
+                         bool sending) {
+  const char *what = sending ? "send_blocks" : "recv_blocks";
+  if (int rc = check_blocks_args(pool, comm, d_ids, n, d_staging, staging_bytes, layers_per_msg, what)) return rc;
+  if (n == 0) return EMM_OK;
+  NcclApi *api;
+  if (int rc = nccl_api(&api)) return rc;
+  emm_ctx *ctx = pool->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  if (int rc = transport_setup(ctx)) return rc;
+
+  const int L = pool->desc.num_layers;
+  const uint64_t layer_bytes = (uint64_t)pool->planes * (uint64_t)n * (uint64_t)pool->page_bytes;
+  const uint64_t slot_bytes = (uint64_t)layers_per_msg * layer_bytes;
+  char *slots[2] = {(char *)d_staging, (char *)d_staging + slot_bytes};
+  cudaStream_t user = (cudaStream_t)stream, copy = ctx->copy_stream, wire = ctx->wire_stream;
+
+  // Everything below is ordered after what the caller has queued on `stream`.
+  EMM_CUDA(cudaEventRecord(ctx->ev_entry, user));
+  EMM_CUDA(cudaStreamWaitEvent(copy, ctx->ev_entry, 0));
+  EMM_CUDA(cudaStreamWaitEvent(wire, ctx->ev_entry, 0));
+
+  int c = 0;
+  for (int begin = 0; begin < L; begin += layers_per_msg, ++c) {
+    const int count = std::min(layers_per_msg, L - begin);
+    const uint64_t bytes = (uint64_t)count * layer_bytes;
+    const int s = c & 1;
+    if (sending) {
+      // pack message c once the send that last read this slot is done, then put it on the wire
+      if (c >= 2) EMM_CUDA(cudaStreamWaitEvent(copy, ctx->ev_wired[s], 0));
+      if (int rc = packed_copy(pool, true, begin, count, d_ids, n, slots[s], bytes, copy)) return rc;
+      EMM_CUDA(cudaEventRecord(ctx->ev_copied[s], copy));
+      EMM_CUDA(cudaStreamWaitEvent(wire, ctx->ev_copied[s], 0));
+      EMM_NCCL(api, api->send(slots[s], (size_t)bytes, kNcclInt8, peer, comm, wire));
+      EMM_CUDA(cudaEventRecord(ctx->ev_wired[s], wire));
+    } else {
+      // receive message c once the unpack that last read this slot is done, then scatter it
+      if (c >= 2) EMM_CUDA(cudaStreamWaitEvent(wire, ctx->ev_copied[s], 0));
+      EMM_NCCL(api, api->recv(slots[s], (size_t)bytes, kNcclInt8, peer, comm, wire));
+      EMM_CUDA(cudaEventRecord(ctx->ev_wired[s], wire));
+      EMM_CUDA(cudaStreamWaitEvent(copy, ctx->ev_wired[s], 0));
+      if (int rc = packed_copy(pool, false, begin, count, d_ids, n, slots[s], bytes, copy)) return rc;
+      EMM_CUDA(cudaEventRecord(ctx->ev_copied[s], copy));
+    }
+  }
+  // Join both helper streams back into the caller's stream.
+  EMM_CUDA(cudaEventRecord(ctx->ev_done[0], copy));
+  EMM_CUDA(cudaEventRecord(ctx->ev_done[1], wire));
+  EMM_CUDA(cudaStreamWaitEvent(user, ctx->ev_done[0], 0));
+  EMM_CUDA(cudaStreamWaitEvent(user, ctx->ev_done[1], 0));
+  return EMM_OK;
+}
+
+int emm_send_blocks(emm_pool *pool, void *comm, int peer, const int32_t *d_ids, int32_t n,
+                    void *d_staging, uint64_t staging_bytes, int32_t layers_per_msg, void *stream) {
+  return staged_blocks(pool, comm, peer, d_ids, n, d_staging, staging_bytes, layers_per_msg, stream, true);
+}
+
+int emm_recv_blocks(emm_pool *pool, void *comm, int peer, const int32_t *d_ids, int32_t n,
+                    void *d_staging, uint64_t staging_bytes, int32_t layers_per_msg, void *stream) {
+  return staged_blocks(pool, comm, peer, d_ids, n, d_staging, staging_bytes, layers_per_msg, stream, false);
+}
 
 // ---------------------------------------------------------------------------
 // Gather without any allocation (see emm_gather_noalloc in emm_kv.h)

@@ -88,6 +88,7 @@ class V0Worker:
         self.latest_swap_out_event: Optional[torch.cuda.Event] = None
         self._xfer_stream = torch.cuda.Stream(self.device)
         self._staging: Optional[torch.Tensor] = None  # flat byte ring for the staged NCCL path
+        self._nccl_comm: Optional[int] = None         # library-owned communicator (init_native_nccl)
         if kv_cache is not None:
             self.bind_kv_cache(kv_cache)
 
@@ -285,6 +286,19 @@ class V0Worker:
             self.global_rank = dist.get_rank()
         return True
 
+    def init_native_nccl(self) -> bool:
+        """Creates a communicator owned by the C library over the ranks of the process group
+        (the unique id travels through torch.distributed). With it, p2p_send_kv / p2p_recv_kv run
+        their pack -> send / receive -> unpack pipelines inside the library on its own streams."""
+        if not self.nccl_pg_initialized:
+            return False
+        world = dist.get_world_size(self.process_group)
+        rank = dist.get_rank(self.process_group)
+        box = [self.ctx.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=self.process_group)
+        self._nccl_comm = self.ctx.nccl_comm_init(box[0], world, rank)
+        return True
+
     def get_global_rank(self) -> int:
         return self.global_rank if self.global_rank is not None else -1
 
@@ -318,6 +332,15 @@ class V0Worker:
             ids = pool.upload_ids(pool._validated(_lib_ids(block_indices)))
             chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
             slots = self._staging_views(pool, n, chunks)
+            if self._nccl_comm is not None:
+                with _range("emm.p2p_send_kv"):
+                    self._staging_views(pool, n, chunks)
+                    pool.send_blocks(self._nccl_comm, dst_rank, ids, self._staging, chunks[0][1])
+                torch.cuda.synchronize(self.device)
+                rc, detail = self.ctx.status()
+                if rc != _lib.OK:
+                    return {"error": f"send failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+                return {"bytes": pool.packed_bytes(n), "blocks": n}
             main = torch.cuda.current_stream(self.device)
             self._xfer_stream.wait_stream(main)
             with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_send_kv"):
@@ -347,6 +370,15 @@ class V0Worker:
             ids = pool.upload_ids(pool._validated(_lib_ids(block_indices), unique=True))
             chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
             slots = self._staging_views(pool, n, chunks)
+            if self._nccl_comm is not None:
+                with _range("emm.p2p_recv_kv"):
+                    self._staging_views(pool, n, chunks)
+                    pool.recv_blocks(self._nccl_comm, src_rank, ids, self._staging, chunks[0][1])
+                torch.cuda.synchronize(self.device)
+                rc, detail = self.ctx.status()
+                if rc != _lib.OK:
+                    return {"error": f"recv failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+                return {"bytes": pool.packed_bytes(n), "blocks": n}
             main = torch.cuda.current_stream(self.device)
             self._xfer_stream.wait_stream(main)
             with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_recv_kv"):

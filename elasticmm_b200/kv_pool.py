@@ -103,6 +103,44 @@ class Context:
         _lib.check(self._lib.emm_ipc_open(self._h, handle, C.c_uint64(offset), C.byref(out)))
         return int(out.value)
 
+    # -- NCCL communicator owned by the library ------------------------------------
+    def nccl_unique_id(self) -> bytes:
+        """A fresh NCCL unique id (rank 0 makes it and ships it to the other ranks)."""
+        buf = C.create_string_buffer(_lib.NCCL_UNIQUE_ID_BYTES)
+        _lib.check(self._lib.emm_nccl_unique_id(buf))
+        return bytes(buf.raw)
+
+    def nccl_comm_init(self, unique_id: bytes, nranks: int, rank: int) -> int:
+        """Collective: every rank calls it with the same id. Returns the ncclComm_t as an int."""
+        comm = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.emm_nccl_comm_init(self._h, unique_id, nranks, rank, C.byref(comm)))
+        return int(comm.value)
+
+    def nccl_comm_destroy(self, comm: int) -> None:
+        _lib.check(self._lib.emm_nccl_comm_destroy(C.c_void_p(comm)))
+
+    def send_packed(self, comm: int, buf: torch.Tensor, peer: int) -> None:
+        """Stream-ordered ncclSend of a contiguous device tensor's bytes."""
+        _lib.check(self._lib.emm_send_packed(C.c_void_p(comm), C.c_void_p(buf.data_ptr()),
+                                             buf.numel() * buf.element_size(), peer,
+                                             C.c_void_p(_stream_ptr(self.device))))
+
+    def recv_packed(self, comm: int, buf: torch.Tensor, peer: int) -> None:
+        _lib.check(self._lib.emm_recv_packed(C.c_void_p(comm), C.c_void_p(buf.data_ptr()),
+                                             buf.numel() * buf.element_size(), peer,
+                                             C.c_void_p(_stream_ptr(self.device))))
+
+    def exchange(self, comm: int, ops: Sequence[Tuple[bool, torch.Tensor, int]]) -> None:
+        """One grouped exchange; ops are (is_send, contiguous device tensor, peer)."""
+        n = len(ops)
+        flags = (C.c_int32 * n)(*[1 if o[0] else 0 for o in ops])
+        bufs = (C.c_void_p * n)(*[o[1].data_ptr() for o in ops])
+        sizes = (C.c_uint64 * n)(*[o[1].numel() * o[1].element_size() for o in ops])
+        peers = (C.c_int32 * n)(*[o[2] for o in ops])
+        _lib.check(self._lib.emm_exchange(C.c_void_p(comm), n, flags, bufs, sizes, peers,
+                                          C.c_void_p(_stream_ptr(self.device))))
+
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h:
             self._lib.emm_ctx_destroy(self._h)
@@ -366,6 +404,25 @@ class KVPool:
             raise _lib.EmmError(_lib.ERR_LENGTH, "src_ids and dst_ids differ in length")
         _lib.check(lib.emm_copy_blocks_h(self._h, dst._h, hs.ctypes.data_as(C.c_void_p),
                                          hd.ctypes.data_as(C.c_void_p), hs.shape[0], st))
+
+    # -- staged transport over a library-owned or host-owned ncclComm_t --------------
+    def send_blocks(self, comm: int, peer: int, ids: torch.Tensor, staging: torch.Tensor,
+                    layers_per_msg: int) -> None:
+        """Pack -> ncclSend pipeline of all layers in messages of `layers_per_msg` layers."""
+        self._check_table(ids, self.device)
+        _lib.check(self.ctx._lib.emm_send_blocks(
+            self._h, C.c_void_p(comm), peer, C.c_void_p(ids.data_ptr()), ids.numel(),
+            C.c_void_p(staging.data_ptr()), staging.numel() * staging.element_size(), layers_per_msg,
+            C.c_void_p(_stream_ptr(self.device))))
+
+    def recv_blocks(self, comm: int, peer: int, ids: torch.Tensor, staging: torch.Tensor,
+                    layers_per_msg: int) -> None:
+        """ncclRecv -> unpack pipeline, the mirror of send_blocks."""
+        self._check_table(ids, self.device)
+        _lib.check(self.ctx._lib.emm_recv_blocks(
+            self._h, C.c_void_p(comm), peer, C.c_void_p(ids.data_ptr()), ids.numel(),
+            C.c_void_p(staging.data_ptr()), staging.numel() * staging.element_size(), layers_per_msg,
+            C.c_void_p(_stream_ptr(self.device))))
 
     # -- per-token append ------------------------------------------------------
     def _check_kv(self, key: torch.Tensor, value: torch.Tensor, slot_mapping: torch.Tensor,

@@ -56,7 +56,8 @@ enum emm_status {
   EMM_ERR_DUPLICATE = 7,  /* duplicate destination ids (write order undefined) */
   EMM_ERR_OVERLAP = 8,    /* source and destination id sets overlap in one pool */
   EMM_ERR_TOO_LARGE = 9,  /* request exceeds a fixed capacity */
-  EMM_ERR_NOMEM = 10      /* host or device allocation failed */
+  EMM_ERR_NOMEM = 10,     /* host or device allocation failed */
+  EMM_ERR_NCCL = 11       /* the NCCL library is missing or one of its calls failed */
 };
 
 typedef struct emm_pool_desc {
@@ -259,6 +260,47 @@ int emm_append_all_layers(emm_pool *pool, const void *d_key, const void *d_value
 int emm_compact_plan(const int64_t *table_ids, int64_t n_ids, int64_t num_blocks,
                      int64_t *new_table_ids, int64_t *move_src, int64_t *move_dst,
                      int64_t *n_moves);
+
+/* ---- staged transport over NCCL (multi-GPU, one process per GPU) ------- */
+
+/* The NCCL entry points are resolved at run time from the libnccl.so.2 the
+ * process already has loaded (or can load); the library does not link NCCL.
+ * `comm` below is an ncclComm_t passed as void*: one made by
+ * emm_nccl_comm_init, or any communicator the host application owns. */
+#define EMM_NCCL_UNIQUE_ID_BYTES 128
+/* Rank 0 creates the id and ships it to the other ranks by any host channel;
+ * the reference rendezvous is tcp://127.0.0.1:29600
+ * (elasticmm/engine/v0/nccl_coordinator.py:179-186, worker.py:225-230). */
+int emm_nccl_unique_id(unsigned char id[EMM_NCCL_UNIQUE_ID_BYTES]);
+/* Collective over all `nranks` ranks (ncclCommInitRank) with ctx's device current. */
+int emm_nccl_comm_init(emm_ctx *ctx, const unsigned char id[EMM_NCCL_UNIQUE_ID_BYTES], int nranks,
+                       int rank, void **comm);
+int emm_nccl_comm_destroy(void *comm);
+
+/* Stream-ordered send / receive of a packed buffer (bytes). Replace the
+ * per-layer torch.distributed.send / recv of p2p_send_kv / p2p_recv_kv
+ * (elasticmm/engine/v0/worker.py:681,718,816). */
+int emm_send_packed(void *comm, const void *d_buf, uint64_t bytes, int peer, void *stream);
+int emm_recv_packed(void *comm, void *d_buf, uint64_t bytes, int peer, void *stream);
+/* One grouped exchange (ncclGroupStart .. ncclGroupEnd): operation k sends
+ * (is_send[k] != 0) or receives bytes[k] bytes at bufs[k] to / from peers[k].
+ * This is the all-to-all-v step of a rebalancing round; the reference has no
+ * collective of this kind. */
+int emm_exchange(void *comm, int32_t n_ops, const int32_t *is_send, void *const *bufs,
+                 const uint64_t *bytes, const int32_t *peers, void *stream);
+
+/* Whole pipelines, ordered after `stream` on entry and joined back into it on
+ * return (asynchronous to the host): the L layers move in messages of
+ * `layers_per_msg` layers through the two halves of `d_staging`
+ * (`staging_bytes` >= 2 * layers_per_msg * 2 * n * page); packing message c+1
+ * overlaps sending message c, receiving c+1 overlaps unpacking c. Both ends
+ * must pass the same n and layers_per_msg. These are p2p_send_kv and
+ * p2p_recv_kv (elasticmm/engine/v0/worker.py:665-731) without the per-layer
+ * serialisation. */
+int emm_send_blocks(emm_pool *pool, void *comm, int peer, const int32_t *d_ids, int32_t n,
+                    void *d_staging, uint64_t staging_bytes, int32_t layers_per_msg, void *stream);
+int emm_recv_blocks(emm_pool *pool, void *comm, int peer, const int32_t *d_ids, int32_t n,
+                    void *d_staging, uint64_t staging_bytes, int32_t layers_per_msg, void *stream);
 
 /* ---- peer mapping (multi-GPU, one process per GPU) --------------------- */
 

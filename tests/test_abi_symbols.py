@@ -30,8 +30,8 @@ def test_abi_version_and_status_strings():
     lib = _lib.load()
     assert lib.emm_abi_version() == 1
     assert lib.emm_status_string(_lib.OK) == b"ok"
-    seen = {lib.emm_status_string(c) for c in range(0, 11)}
-    assert len(seen) == 11 and b"unknown status" not in seen
+    seen = {lib.emm_status_string(c) for c in range(0, 12)}
+    assert len(seen) == 12 and b"unknown status" not in seen
     assert lib.emm_status_string(99) == b"unknown status"
 
 

@@ -77,6 +77,34 @@ def _worker_main(rank, world, port, out_dir):
         results["nccl_bytes"] = mgr.last_result["bytes"]
     dist.barrier()
 
+    # 1b. the same through a communicator owned by the C library (pipelines run inside the library)
+    w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    results["native_init_ok"] = w.init_native_nccl()
+    mgr = V0KVTransferManager(transfer_method=TransferMethod.NCCL)
+    mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+    before = w.ctx.launch_count
+    oks = [mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs]
+    results["native_nccl_ok"] = all(oks) and w.ctx.launch_count > before
+    if rank == 1:
+        results["native_nccl_exact"] = same(w, expect(reqs))
+    # raw entries: one message each way, then both ways in one grouped exchange
+    comm = w._nccl_comm
+    mine = torch.full((1 << 20,), float(rank + 1), dtype=torch.float32, device=dev)
+    theirs = torch.zeros_like(mine)
+    if rank == 0:
+        w.ctx.send_packed(comm, mine, 1)
+        w.ctx.recv_packed(comm, theirs, 1)
+    else:
+        w.ctx.recv_packed(comm, theirs, 0)
+        w.ctx.send_packed(comm, mine, 0)
+    torch.cuda.synchronize()
+    results["packed_exact"] = bool(torch.all(theirs == float(2 - rank)))
+    theirs.zero_()
+    w.ctx.exchange(comm, [(True, mine, 1 - rank), (False, theirs, 1 - rank)])
+    torch.cuda.synchronize()
+    results["exchange_packed_exact"] = bool(torch.all(theirs == float(2 - rank)))
+    dist.barrier()
+
     # 2. direct peer stores: map the sink's pool into the source, one launch per request
     w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
     handles = [None] * world
