@@ -36,7 +36,7 @@ class TransferMethod(Enum):
     CUDA_IPC = "cuda_ipc"      # accepted as an alias of B200_PEER
     NCCL = "nccl"              # staged: pack -> NCCL send/recv -> unpack, pipelined by layer chunk
     P2P_COPY = "p2p_copy"      # extract on the source, write on the sink (both workers in this process)
-    STAGED_COPY = "staged_copy"  # not implemented in the reference either (a sleep); refused here
+    STAGED_COPY = "staged_copy"  # gather -> pinned host buffer -> scatter (a sleep stub in the reference)
     B200_PEER = "b200_peer"    # one kernel over peer-mapped pools: the sink loads (default) or the source stores
 
 
@@ -58,6 +58,7 @@ class V0KVTransferManager:
         self.total_transfer_time = 0.0
         self.total_bytes_transferred = 0
         self.first_transfer_done = False
+        self._host_stage: Optional[torch.Tensor] = None  # pinned buffer of the staged_copy method
         # batching: small transfers of one (source, sink) pair are merged into one table
         self._transfer_queue: Dict[tuple, List[tuple]] = {}
         self._last_flush_time: Dict[tuple, float] = {}
@@ -149,6 +150,23 @@ class V0KVTransferManager:
                 if rc != 0:
                     return {"error": "device reported a bad block id", "bytes": 0, "blocks": 0}
             return res
+        if method == TransferMethod.STAGED_COPY:
+            # Through pinned host memory (the reference only sketches this method with a sleep,
+            # elasticmm/engine/v0/kv_transfer.py:821-841): gather on the source GPU, one D2H and
+            # one H2D copy of the packed buffer, scatter on the sink GPU. For pairs without a
+            # peer mapping or a process group; bound by PCIe.
+            if src is None or dst is None:
+                return {"error": "staged_copy needs both workers in this process", "bytes": 0, "blocks": 0}
+            data = src.extract_kv_blocks(src_blocks)
+            nbytes = data.numel() * data.element_size()
+            if self._host_stage is None or self._host_stage.numel() < nbytes:
+                self._host_stage = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+            host = self._host_stage[:nbytes].view(data.dtype).view(data.shape)
+            host.copy_(data, non_blocking=True)
+            torch.cuda.synchronize(src.device)
+            dst.write_kv_blocks(dst_blocks, host.to(dst.device, non_blocking=True))
+            torch.cuda.synchronize(dst.device)
+            return {"bytes": nbytes, "blocks": len(src_blocks)}
         return {"error": f"transfer method {self.transfer_method.value} is not implemented",
                 "bytes": 0, "blocks": 0}
 

@@ -188,6 +188,17 @@ class MigrationPlan:
         self._tables[(src_rank, dst_rank)] = (src, dst)
         return src, dst
 
+    def tables_np(self, src_rank: int, dst_rank: int):
+        """The same two tables as contiguous int64 arrays (made once; what the C ABI takes)."""
+        import numpy as np
+
+        key = ("np", src_rank, dst_rank)
+        cached = self._tables.get(key)
+        if cached is None:
+            s, d = self.tables(src_rank, dst_rank)
+            cached = self._tables[key] = (np.asarray(s, dtype=np.int64), np.asarray(d, dtype=np.int64))
+        return cached
+
     def outgoing(self, rank: int) -> List[int]:
         return [d for s, d in self.pairs() if s == rank]
 

@@ -564,7 +564,7 @@ class V0Worker:
             main = torch.cuda.current_stream(self.device)
             used = []
             for peer in peers:
-                src_ids, dst_ids = plan.tables(peer, rank)
+                src_ids, dst_ids = plan.tables_np(peer, rank)
                 stream = self._peer_streams.get(peer)
                 if stream is None:
                     stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
@@ -580,7 +580,7 @@ class V0Worker:
         elif method == "push":
             # A source pushes to one sink at a time, sources starting at different sinks.
             for peer in plan.push_order(rank):
-                src_ids, dst_ids = plan.tables(rank, peer)
+                src_ids, dst_ids = plan.tables_np(rank, peer)
                 res = self.p2p_push_kv(peer, src_ids, dst_ids)
                 if "error" in res:
                     return res

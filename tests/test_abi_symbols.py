@@ -72,3 +72,12 @@ def test_context_creation_fails_loudly_without_a_device():
         get_context(0)
     with pytest.raises(RuntimeError, match="no CPU path"):
         V0Worker()
+
+
+def test_nccl_entries_validate_arguments_without_a_gpu():
+    lib = _lib.load()
+    assert lib.emm_send_packed(None, None, 16, 0, None) == _lib.ERR_BAD_ARG
+    assert lib.emm_recv_packed(None, None, 16, 0, None) == _lib.ERR_BAD_ARG
+    assert lib.emm_exchange(None, 1, None, None, None, None, None) == _lib.ERR_BAD_ARG
+    assert lib.emm_nccl_comm_destroy(None) == _lib.OK
+    assert lib.emm_send_blocks(None, None, 0, None, 0, None, 0, 1, None) == _lib.ERR_BAD_ARG

@@ -56,7 +56,8 @@ def test_extract_write_layout_like_the_reference():
     assert empty.switch_role(EngineStage.DECODING) and empty.get_stage() == EngineStage.DECODING
 
 
-@pytest.mark.parametrize("method", [TransferMethod.P2P_COPY, TransferMethod.B200_PEER, TransferMethod.CUDA_IPC])
+@pytest.mark.parametrize("method", [TransferMethod.P2P_COPY, TransferMethod.B200_PEER, TransferMethod.CUDA_IPC,
+                                    TransferMethod.STAGED_COPY])
 def test_transfer_manager_in_process(method):
     src, src_cpu = make_worker(2)
     dst, dst_cpu = make_worker(0, guard=True)
