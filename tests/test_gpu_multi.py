@@ -160,22 +160,22 @@ def _worker_main(rank, world, port, out_dir):
         results["broadcast_exact"] = same(wb, expect(reqs[:1]))
     dist.barrier()
 
-    # 4. exchange: both ranks are source and sink at once (peer method only)
+    # 4. exchange: both ranks are source and sink at once; each pulls from the other's source pool
     w3, _ = fresh(70, guard=False)
     sink_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0,
                                    fill="guard")
     sink = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
                     kv_cache=[t.to(dev) for t in sink_cpu])
+    sink.init_global_nccl()
     h3 = [None] * world
-    dist.all_gather_object(h3, (sink.get_ipc_handles(), sink.get_pool_desc()))
-    w3.init_global_nccl()
+    dist.all_gather_object(h3, (w3.get_ipc_handles(), w3.get_pool_desc()))
     for peer in range(world):
         if peer != rank:
-            w3.attach_peer_pool(peer, h3[peer][0], h3[peer][1])
+            sink.attach_peer_pool(peer, h3[peer][0], h3[peer][1])
     plan = MigrationPlan([Transfer(f"{rid}-{src}", src, 1 - src, tuple(s), tuple(d))
                           for src in (0, 1) for rid, s, d in _requests(3 + src)])
-    res = w3.migrate(plan, method="push")
-    results["exchange_ok"] = "error" not in res
+    res = sink.migrate(plan, method="pull")
+    results["exchange_ok"] = "error" not in res and res["blocks"] > 0
     dist.barrier()
     mine = [(rid, s, d) for rid, s, d in _requests(3 + (1 - rank))]
     results["exchange_exact"] = same(sink, expect(mine))
