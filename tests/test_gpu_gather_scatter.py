@@ -174,3 +174,31 @@ def test_random_round_trips_many_requests(ctx):
         pos += n
     assert_clean(ctx)
     assert pools_equal(dst.layers, dst_cpu)
+
+
+def test_device_table_entries_replay_from_a_cuda_graph(ctx):
+    """gather -> scatter -> block copy captured once and replayed with new table contents."""
+    case = cases.KV_CASES[12]   # 32 KiB pages
+    src_cpu, dst_cpu = cases.build_pools(case)
+    src, dst = KVPool(to_gpu(src_cpu), ctx), KVPool(to_gpu(dst_cpu), ctx)
+    n = len(case["src_ids"])
+    s_dev, d_dev = src.upload_ids(case["src_ids"]), dst.upload_ids(case["dst_ids"])
+    packed = src.new_packed(n)
+    src.gather(s_dev, out=packed)          # first use outside capture (sets the kernel's shared-memory limit)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            src.gather(s_dev, out=packed)
+            dst.scatter(d_dev, packed)
+    for trial in range(2):
+        g = torch.Generator().manual_seed(trial)
+        s_ids = torch.randperm(case["NB"], generator=g)[:n].tolist()
+        d_ids = torch.randperm(case["NB"], generator=g)[:n].tolist()
+        s_dev.copy_(torch.tensor(s_ids, dtype=torch.int32))
+        d_dev.copy_(torch.tensor(d_ids, dtype=torch.int32))
+        graph.replay()
+        kv_oracle.write_kv_blocks(dst_cpu, d_ids, kv_oracle.extract_kv_blocks(src_cpu, s_ids))
+    assert_clean(ctx)
+    assert pools_equal(dst.layers, dst_cpu)
