@@ -214,6 +214,8 @@ class CpuPath:
 
         self.oracle = kv_oracle
         self.wname = wname
+        # torchrun pins OMP_NUM_THREADS to 1 per rank; the CPU legs run on one rank only and may use every core
+        torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
         w = self.w = WORKLOADS[wname]
         self.nb = nb = min(w["NB"], max(64, int(3 * GIB // block_bytes(w))))
         dt = DT[w["dtype"]]
