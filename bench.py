@@ -630,33 +630,30 @@ def bench_multi(args):
     per_src = {s: [i for i in range(len(counts)) if i % len(sources) == k] for k, s in enumerate(sources)}
 
     def build_plans():
-        """Greedy waves: in each wave every source takes its next requests, in order, while they fit its
-        own pool and the pool of the sink they are assigned to."""
+        """First-fit waves: in each wave every source takes, in order, each of its remaining requests
+        that still fits its own pool and the pool of the sink the request is assigned to (requests are
+        independent, so their order is free). Fuller waves mean fewer barriers and less imbalance."""
         out = []
-        cursor = {s: 0 for s in sources}
+        remaining = {s: list(per_src[s]) for s in sources}
         wv = 0
-        while any(cursor[s] < len(per_src[s]) for s in sources):
+        while any(remaining.values()):
             plan = MigrationPlan()
             sink_used = {d: 0 for d in sinks}
             sink_perm = {d: torch.randperm(w["NB"], generator=torch.Generator().manual_seed(77 * wv + d)).tolist()
                          for d in sinks}
-            # sinks are shared: give each source an equal share of every sink per wave
-            share = w["NB"] // len(sources)
             for s in sources:
                 perm = torch.randperm(w["NB"], generator=torch.Generator().manual_seed(1000 * wv + s)).tolist()
-                pos = 0
-                used_here = {d: 0 for d in sinks}
-                while cursor[s] < len(per_src[s]):
-                    i = per_src[s][cursor[s]]
+                pos, later = 0, []
+                for i in remaining[s]:
                     d, n = sinks[assign[i]], counts[i]
-                    if pos + n > w["NB"] or used_here[d] + n > max(share, n) or sink_used[d] + n > w["NB"]:
-                        break
+                    if pos + n > w["NB"] or sink_used[d] + n > w["NB"]:
+                        later.append(i)
+                        continue
                     plan.add(Transfer(f"req{i}", s, d, tuple(perm[pos:pos + n]),
                                       tuple(sink_perm[d][sink_used[d]:sink_used[d] + n])))
                     pos += n
                     sink_used[d] += n
-                    used_here[d] += n
-                    cursor[s] += 1
+                remaining[s] = later
             assert plan.transfers, "a request does not fit an empty wave"
             out.append(plan)
             wv += 1
