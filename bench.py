@@ -758,6 +758,17 @@ def bench_multi(args):
                                           "ms_per_step": round(ms_nn / nccl_steps, 3),
                                           "path": "emm_send_blocks / emm_recv_blocks: pack -> ncclSend, ncclRecv -> "
                                                   "unpack on library streams"}
+        def step_a2a():
+            for plan in plans:
+                res = worker.migrate(plan, method="alltoall")
+                assert "error" not in res, res
+
+        ms_a = max_ms(timed(step_a2a, nccl_steps, 2, device, barrier))
+        variants["nccl_alltoall_pipelined"] = {
+            "value": round(payload * nccl_steps / (ms_a / 1e3) / 1e9, 2), "unit": "GB/s",
+            "ms_per_step": round(ms_a / nccl_steps, 3),
+            "path": "per layer chunk: one gather for all sinks, one grouped ncclSend/ncclRecv exchange among all "
+                    "ranks, one scatter for all sources; three streams, two staging slots"}
     except Exception as e:
         variants["nccl_staged_native"] = {"error": f"{type(e).__name__}: {e}"}
 

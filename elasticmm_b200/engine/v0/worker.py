@@ -89,6 +89,7 @@ class V0Worker:
         self._xfer_stream = torch.cuda.Stream(self.device)
         self._staging: Optional[torch.Tensor] = None  # flat byte ring for the staged NCCL path
         self._nccl_comm: Optional[int] = None         # library-owned communicator (init_native_nccl)
+        self._a2a: Optional[Dict[str, Any]] = None    # streams and staging of the all-to-all migration
         if kv_cache is not None:
             self.bind_kv_cache(kv_cache)
 
@@ -544,7 +545,10 @@ class V0Worker:
         method "pull" (default; "peer" is an alias): each sink launches one
         direct-load kernel per source, side by side with capped grids, then all
         ranks meet at a barrier. method "push": each source launches one
-        direct-store kernel per sink instead, one sink at a time. method "nccl": per pair, the staged pipeline of
+        direct-store kernel per sink instead, one sink at a time. method "alltoall":
+        per layer chunk, one gather for all sinks, one grouped NCCL exchange with every
+        peer, one scatter for all sources, pipelined over the chunks (needs
+        init_native_nccl). method "nccl": per pair, the staged pipeline of
         p2p_send_kv / p2p_recv_kv; every rank walks the pairs in the plan's one
         global order (sources start at different sinks), which rules out a
         circular wait.
@@ -591,6 +595,8 @@ class V0Worker:
             dist.barrier(group=self.process_group)
             if rc != _lib.OK:
                 return {"error": f"{method} failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+        elif method == "alltoall":
+            return self._migrate_alltoall(plan)
         elif method == "nccl":
             if plan.outgoing(rank) and plan.incoming(rank):
                 return {"error": "nccl migration needs each rank to be a pure source or a pure sink; "
@@ -608,6 +614,133 @@ class V0Worker:
         else:
             raise ValueError(f"unknown migration method {method!r}")
         return {"bytes": moved * pool.block_bytes(), "blocks": moved}
+
+
+def _migrate_alltoall(self, plan: MigrationPlan) -> Dict[str, Any]:
+    """Per-layer pipelined all-to-all of packed pages over the library's NCCL communicator.
+
+    Every rank of the plan calls this. For each chunk of layers a source packs the blocks of all
+    its sinks with one gather (tables concatenated in sink order, so each sink's pages of one
+    layer and plane are one contiguous segment), all ranks run one grouped exchange in which a
+    source sends those segments and a sink receives the segments of all its sources into one
+    staging buffer, and the sink unpacks them with one scatter over its concatenated destination
+    table. Packing chunk c+1, exchanging chunk c and unpacking chunk c-1 overlap on three streams
+    with two staging slots per direction. A rank may be source and sink at once: its sends and
+    receives of a chunk share one NCCL group.
+    """
+    if self._nccl_comm is None:
+        return {"error": "alltoall migration needs init_native_nccl()", "bytes": 0, "blocks": 0}
+    rank = self.get_global_rank()
+    pool = self._require_pool()
+    page = pool.page_bytes
+    sinks = sorted(plan.outgoing(rank))
+    sources = sorted(plan.incoming(rank))
+    out_tabs = [plan.tables_np(rank, d)[0] for d in sinks]
+    in_tabs = [plan.tables_np(s, rank)[1] for s in sources]
+    n_out = [len(t) for t in out_tabs]
+    n_in = [len(t) for t in in_tabs]
+    N_out, N_in = sum(n_out), sum(n_in)
+    # one chunk schedule for everybody: sized by the busiest rank of the plan
+    totals: Dict[int, int] = {}
+    for t in plan.transfers:
+        totals[("o", t.src_rank)] = totals.get(("o", t.src_rank), 0) + len(t.src_blocks)
+        totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
+    n_ref = max(totals.values()) if totals else 0
+    chunks = plan_chunks(pool.num_layers, n_ref, page)
+    if not chunks:
+        dist.barrier(group=self.process_group)
+        return {"bytes": 0, "blocks": 0}
+    lc_max = max_chunk_layers(chunks)
+    import numpy as np
+
+    ctx = self.ctx
+    main = torch.cuda.current_stream(self.device)
+    if self._a2a is None:
+        self._a2a = {"pack": torch.cuda.Stream(self.device), "wire": torch.cuda.Stream(self.device),
+                     "unpack": torch.cuda.Stream(self.device), "out": None, "in": None}
+    a2a = self._a2a
+    need_out = 2 * pool.packed_bytes(N_out, lc_max)
+    need_in = 2 * pool.packed_bytes(N_in, lc_max)
+    if N_out and (a2a["out"] is None or a2a["out"].numel() < need_out):
+        a2a["out"] = torch.empty(need_out, dtype=torch.uint8, device=self.device)
+    if N_in and (a2a["in"] is None or a2a["in"].numel() < need_in):
+        a2a["in"] = torch.empty(need_in, dtype=torch.uint8, device=self.device)
+    ids_out = pool.upload_ids(pool._validated(np.concatenate(out_tabs))) if N_out else None
+    ids_in = pool.upload_ids(pool._validated(np.concatenate(in_tabs), unique=True)) if N_in else None
+    for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
+        st.wait_stream(main)
+    ev_packed = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_wired = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_unpacked = [torch.cuda.Event(), torch.cuda.Event()]
+
+    n_sinks_of = {s: len(plan.outgoing(s)) for s, _ in plan.pairs()}
+    n_sources_of = {d: len(plan.incoming(d)) for _, d in plan.pairs()}
+
+    def whole_chunk(src: int, dst: int) -> bool:
+        """Both ends see this pair's pages of a chunk as one contiguous run (the source has no other
+        sink, the sink no other source), so the chunk travels as one message instead of one per
+        layer and plane. Decided from the plan alone, hence identically on both ends."""
+        return n_sinks_of[src] == 1 and n_sources_of[dst] == 1
+
+    def slot_view(buf, slot, n_total, lc):
+        nbytes = pool.packed_bytes(n_total, lc)
+        half = buf.numel() // 2
+        flat = buf[slot * half: slot * half + nbytes]
+        return flat, pool._logical(flat.view(pool.dtype).view(pool.packed_shape(n_total, lc)))
+
+    with _range("emm.migrate_alltoall"):
+        for c, (begin, count) in enumerate(chunks):
+            slot = c & 1
+            ops = []
+            if N_out:
+                flat_out, view_out = slot_view(a2a["out"], slot, N_out, count)
+                with torch.cuda.stream(a2a["pack"]):
+                    if c >= 2:
+                        a2a["pack"].wait_event(ev_wired[slot])       # the exchange that read this slot is done
+                    pool.gather(ids_out, out=view_out, layer_begin=begin, layer_count=count)
+                    ev_packed[slot].record(a2a["pack"])
+                a2a["wire"].wait_event(ev_packed[slot])
+                off = 0
+                for d, n in zip(sinks, n_out):
+                    if whole_chunk(rank, d):                         # the pair's chunk is one contiguous run
+                        ops.append((True, flat_out, d))
+                    else:
+                        for lp in range(count * pool.num_planes):    # (layer, plane) rows of the packed buffer
+                            start = (lp * N_out + off) * page
+                            ops.append((True, flat_out[start:start + n * page], d))
+                    off += n
+            if N_in:
+                flat_in, view_in = slot_view(a2a["in"], slot, N_in, count)
+                if c >= 2:
+                    a2a["wire"].wait_event(ev_unpacked[slot])        # the scatter that read this slot is done
+                off = 0
+                for s_rank, n in zip(sources, n_in):
+                    if whole_chunk(s_rank, rank):
+                        ops.append((False, flat_in, s_rank))
+                    else:
+                        for lp in range(count * pool.num_planes):
+                            start = (lp * N_in + off) * page
+                            ops.append((False, flat_in[start:start + n * page], s_rank))
+                    off += n
+            with torch.cuda.stream(a2a["wire"]):
+                ctx.exchange(self._nccl_comm, ops)
+                ev_wired[slot].record(a2a["wire"])
+            if N_in:
+                with torch.cuda.stream(a2a["unpack"]):
+                    a2a["unpack"].wait_event(ev_wired[slot])
+                    pool.scatter(ids_in, view_in, layer_begin=begin, layer_count=count)
+                    ev_unpacked[slot].record(a2a["unpack"])
+    for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
+        main.wait_stream(st)
+    torch.cuda.synchronize(self.device)
+    rc, _ = ctx.status()
+    dist.barrier(group=self.process_group)
+    if rc != _lib.OK:
+        return {"error": f"alltoall failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+    return {"bytes": (N_out + N_in) * pool.block_bytes(), "blocks": N_out + N_in}
+
+
+V0Worker._migrate_alltoall = _migrate_alltoall
 
 
 def _lib_ids(ids):

@@ -105,6 +105,29 @@ def _worker_main(rank, world, port, out_dir):
     results["exchange_packed_exact"] = bool(torch.all(theirs == float(2 - rank)))
     dist.barrier()
 
+    # 1c. per-layer pipelined all-to-all over the same communicator: one direction, then both at once
+    wa, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    wa.init_native_nccl()
+    plan_a = MigrationPlan([Transfer(rid, 0, 1, tuple(s), tuple(d)) for rid, s, d in reqs])
+    res = wa.migrate(plan_a, method="alltoall")
+    results["alltoall_ok"] = "error" not in res
+    if rank == 1:
+        results["alltoall_exact"] = same(wa, expect(reqs))
+    dist.barrier()
+    wb2, _ = fresh(70, guard=False)          # every rank holds source data in the lower half of its pool ...
+    wb2.init_native_nccl()
+    half = GEOM["NB"] // 2
+    both = MigrationPlan([Transfer(f"x{src}", src, 1 - src, tuple(range(src, half, 2)),
+                                   tuple(range(half + src, GEOM["NB"], 2))) for src in (0, 1)])
+    before_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 70)
+    res = wb2.migrate(both, method="alltoall")  # ... and receives the peer's blocks into its upper half
+    results["alltoall_both_ok"] = "error" not in res and res["blocks"] == 2 * len(range(0, half, 2))
+    src_ids, dst_ids = both.tables(1 - rank, rank)
+    kv_oracle.write_kv_blocks(before_cpu, dst_ids, kv_oracle.extract_kv_blocks(
+        kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 70), src_ids))
+    results["alltoall_both_exact"] = same(wb2, before_cpu)
+    dist.barrier()
+
     # 2. direct peer stores: map the sink's pool into the source, one launch per request
     w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
     handles = [None] * world
