@@ -43,6 +43,7 @@ OPT_CTAS_PER_SM = 4
 OPT_LDG_UNROLL = 5
 OPT_MAX_CTAS = 6
 OPT_REMOTE_VARIANT = 7
+OPT_L2_HINT = 8
 
 
 class PoolDesc(C.Structure):

@@ -97,6 +97,7 @@ struct emm_ctx {
   int ldg_unroll = 2;
   int max_ctas = 0;
   int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
+  int l2_hint = 0;                    // bulk family: bit 0 loads, bit 1 stores carry an L2 evict-first hint
   int bulk_smem_set = 0;    // dynamic smem limit already applied to the bulk kernel
   IdSlot ring[kRingSlots];
   int next_slot = 0;
@@ -314,7 +315,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(want, cap);
-    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages);
+    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
   } else {
     // A peer or host destination is bound by the link, not by HBM: one CTA per SM
     // already saturates NVLink (measured), and small grids let pushes to several
@@ -507,6 +508,10 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       if (value < 0 || value > (1 << 20)) return fail(EMM_ERR_BAD_ARG, "max CTAs out of range");
       ctx->max_ctas = (int)value;
       return EMM_OK;
+    case EMM_OPT_L2_HINT:
+      if (value < 0 || value > 3) return fail(EMM_ERR_BAD_ARG, "L2 hint must be in [0, 3]");
+      ctx->l2_hint = (int)value;
+      return EMM_OK;
     case EMM_OPT_REMOTE_VARIANT:
       if (value != EMM_COPY_BULK && value != EMM_COPY_LDG)
         return fail(EMM_ERR_BAD_ARG, "remote variant must be EMM_COPY_BULK or EMM_COPY_LDG");
@@ -528,6 +533,7 @@ int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
     case EMM_OPT_LDG_UNROLL: *value = ctx->ldg_unroll; return EMM_OK;
     case EMM_OPT_MAX_CTAS: *value = ctx->max_ctas; return EMM_OK;
     case EMM_OPT_REMOTE_VARIANT: *value = ctx->remote_variant; return EMM_OK;
+    case EMM_OPT_L2_HINT: *value = ctx->l2_hint; return EMM_OK;
     default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
 }
@@ -1342,7 +1348,7 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     }
     const uint64_t want_ctas = (a.total_chunks + warps - 1) / warps;
     const int grid = (int)std::min<uint64_t>(want_ctas, (uint64_t)nd->sm_count * per_sm);
-    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages);
+    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages, 0u);
   } else {
     int64_t chunk = std::min<int64_t>(65536, page);
     a.chunk_bytes = (uint32_t)chunk;

@@ -183,6 +183,28 @@ __device__ __forceinline__ void bulk_store(uint64_t gdst, uint32_t smem_src, uin
                : "memory");
 }
 
+// Variants with an L2 eviction-priority hint (the pages are touched once).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+
+__device__ __forceinline__ void bulk_load_hint(uint32_t smem_dst, uint64_t gsrc, uint32_t bytes,
+                                               uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_store_hint(uint64_t gdst, uint32_t smem_src, uint32_t bytes,
+                                                uint64_t policy) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(gdst),
+               "r"(smem_src), "r"(bytes), "l"(policy)
+               : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -210,7 +232,7 @@ __device__ __forceinline__ void bulk_wait_all() {
 // refills that slot with load j+stages-1. Addresses for the next load are
 // decoded one iteration early so the table read is off the critical path.
 __global__ void __launch_bounds__(kMaxWarps * 32)
-page_copy_bulk(const PageCopyArgs a, const uint32_t stages) {
+page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hint) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t bars[kMaxWarps * kMaxStages];
   __shared__ uint64_t slot_dst[kMaxWarps * kMaxStages];
@@ -227,6 +249,8 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages) {
 
   for (uint32_t s = 0; s < stages; ++s) mbar_init(smem_u32(&my_bars[s]), 1);
   mbar_init_fence();
+  // l2_hint bit 0: loads evict-first, bit 1: stores evict-first
+  const uint64_t policy = l2_hint ? l2_evict_first_policy() : 0;
 
   const uint64_t stream_id = (uint64_t)blockIdx.x * warps + warp;
   const uint64_t stream_step = (uint64_t)gridDim.x * warps;
@@ -240,7 +264,8 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages) {
     my_len[s] = ca.len;
     if (ca.len) {
       mbar_expect_tx(bar, ca.len);
-      bulk_load(ring + s * a.chunk_bytes, ca.src, ca.len, bar);
+      if (l2_hint & 1) bulk_load_hint(ring + s * a.chunk_bytes, ca.src, ca.len, bar, policy);
+      else bulk_load(ring + s * a.chunk_bytes, ca.src, ca.len, bar);
     } else {
       mbar_arrive(bar);  // skipped page: complete the phase with no bytes
     }
@@ -270,7 +295,10 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages) {
       timed_out = true;
       break;
     }
-    if (my_len[s]) bulk_store(my_dst[s], ring + s * a.chunk_bytes, my_len[s]);
+    if (my_len[s]) {
+      if (l2_hint & 2) bulk_store_hint(my_dst[s], ring + s * a.chunk_bytes, my_len[s], policy);
+      else bulk_store(my_dst[s], ring + s * a.chunk_bytes, my_len[s]);
+    }
     bulk_commit();
 
     if (jn < n_mine) {

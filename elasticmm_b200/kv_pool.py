@@ -62,13 +62,15 @@ class Context:
     def configure(self, *, variant: Optional[int] = None, chunk_bytes: Optional[int] = None,
                   stages: Optional[int] = None, warps: Optional[int] = None,
                   ctas_per_sm: Optional[int] = None, ldg_unroll: Optional[int] = None,
-                  max_ctas: Optional[int] = None, remote_variant: Optional[int] = None) -> None:
+                  max_ctas: Optional[int] = None, remote_variant: Optional[int] = None,
+                  l2_hint: Optional[int] = None) -> None:
         """Sets copy-kernel options; None leaves an option as it is."""
         pairs = [
             (_lib.OPT_COPY_VARIANT, variant), (_lib.OPT_CHUNK_BYTES, chunk_bytes),
             (_lib.OPT_STAGES, stages), (_lib.OPT_WARPS, warps),
             (_lib.OPT_CTAS_PER_SM, ctas_per_sm), (_lib.OPT_LDG_UNROLL, ldg_unroll),
             (_lib.OPT_MAX_CTAS, max_ctas), (_lib.OPT_REMOTE_VARIANT, remote_variant),
+            (_lib.OPT_L2_HINT, l2_hint),
         ]
         for opt, val in pairs:
             if val is not None:

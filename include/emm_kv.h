@@ -90,7 +90,8 @@ enum emm_option {
   EMM_OPT_CTAS_PER_SM = 4,   /* resident CTAs per SM the grid is sized for */
   EMM_OPT_LDG_UNROLL = 5,    /* 16-byte loads in flight per thread, LDG variant (1,2,4,8) */
   EMM_OPT_MAX_CTAS = 6,      /* cap on the grid (0 = none) */
-  EMM_OPT_REMOTE_VARIANT = 7 /* family used when a side is a peer GPU's or pinned host memory (default LDG) */
+  EMM_OPT_REMOTE_VARIANT = 7, /* family used when a side is a peer GPU's or pinned host memory (default LDG) */
+  EMM_OPT_L2_HINT = 8         /* bulk variant: bit 0 loads, bit 1 stores carry an L2 evict-first hint (default 0) */
 };
 
 /* ---- library ---------------------------------------------------------- */
