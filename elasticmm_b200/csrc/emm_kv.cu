@@ -317,9 +317,10 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     const int grid = (int)std::min<uint64_t>(want, cap);
     emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
   } else {
-    // A peer or host destination is bound by the link, not by HBM: one CTA per SM
-    // already saturates NVLink (measured), and small grids let pushes to several
-    // sinks run side by side on different streams.
+    // A copy to or from a peer GPU or pinned host memory is bound by the link, not
+    // by HBM: 48 CTAs already saturate NVLink (measured), and side-by-side copies
+    // from several peers only keep the link rate when together they hold at most
+    // one CTA per SM, so the default is one per SM and callers cap it further.
     const int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : (local ? 4 : 1);
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);

@@ -317,85 +317,58 @@ class V0Worker:
             return pool._logical(flat.view(pool.packed_shape(n, layer_count)))
         return buffer_for
 
+    def _staged_transfer(self, sending: bool, peer: int, block_indices: List[int]) -> Dict[str, Any]:
+        """Common body of p2p_send_kv / p2p_recv_kv: chunk schedule, staging ring, then either the
+        library's own pipeline (after init_native_nccl) or the same schedule over torch P2P."""
+        what = "send" if sending else "recv"
+        if not self.nccl_pg_initialized:
+            return {"error": "Global NCCL not initialized", "bytes": 0, "blocks": 0}
+        try:
+            pool = self._require_pool()
+            n = len(block_indices)
+            if n == 0:
+                return {"bytes": 0, "blocks": 0}
+            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices), unique=not sending))
+            chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
+            slots = self._staging_views(pool, n, chunks)
+            with _range(f"emm.p2p_{what}_kv"):
+                if self._nccl_comm is not None:
+                    run = pool.send_blocks if sending else pool.recv_blocks
+                    run(self._nccl_comm, peer, ids, self._staging, chunks[0][1])
+                else:
+                    main = torch.cuda.current_stream(self.device)
+                    self._xfer_stream.wait_stream(main)
+                    with torch.cuda.stream(self._xfer_stream):
+                        if sending:
+                            pipelined_send(
+                                chunks, self._buffer_for(pool, n, slots),
+                                pack=lambda buf, b, c: pool.gather(ids, out=buf, layer_begin=b, layer_count=c),
+                                isend=lambda buf: dist.isend(pool._logical(buf), dst=peer, group=self.process_group))
+                        else:
+                            pipelined_recv(
+                                chunks, self._buffer_for(pool, n, slots),
+                                irecv=lambda buf: dist.irecv(pool._logical(buf), src=peer, group=self.process_group),
+                                unpack=lambda buf, b, c: pool.scatter(ids, buf, layer_begin=b, layer_count=c))
+                    main.wait_stream(self._xfer_stream)
+            torch.cuda.synchronize(self.device)
+            rc, _ = self.ctx.status()
+            if rc != _lib.OK:
+                return {"error": f"{what} failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
+            return {"bytes": pool.packed_bytes(n), "blocks": n}
+        except Exception as e:  # data-path errors are reported, not raised
+            return {"error": f"NCCL {what} failed: {type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+
     def p2p_send_kv(self, dst_rank: int, block_indices: List[int]) -> Dict[str, Any]:
         """Packs the blocks chunk by chunk and sends them to `dst_rank`.
 
         Packing of chunk c+1 overlaps the send of chunk c. The call returns
         after the device has finished, as the reference does.
         """
-        if not self.nccl_pg_initialized:
-            return {"error": "Global NCCL not initialized", "bytes": 0, "blocks": 0}
-        try:
-            pool = self._require_pool()
-            n = len(block_indices)
-            if n == 0:
-                return {"bytes": 0, "blocks": 0}
-            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices)))
-            chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
-            slots = self._staging_views(pool, n, chunks)
-            if self._nccl_comm is not None:
-                with _range("emm.p2p_send_kv"):
-                    self._staging_views(pool, n, chunks)
-                    pool.send_blocks(self._nccl_comm, dst_rank, ids, self._staging, chunks[0][1])
-                torch.cuda.synchronize(self.device)
-                rc, detail = self.ctx.status()
-                if rc != _lib.OK:
-                    return {"error": f"send failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
-                return {"bytes": pool.packed_bytes(n), "blocks": n}
-            main = torch.cuda.current_stream(self.device)
-            self._xfer_stream.wait_stream(main)
-            with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_send_kv"):
-                pipelined_send(
-                    chunks, self._buffer_for(pool, n, slots),
-                    pack=lambda buf, b, c: pool.gather(ids, out=buf, layer_begin=b, layer_count=c),
-                    isend=lambda buf: dist.isend(pool._logical(buf), dst=dst_rank, group=self.process_group),
-                )
-            main.wait_stream(self._xfer_stream)
-            torch.cuda.synchronize(self.device)
-            rc, detail = self.ctx.status()
-            if rc != _lib.OK:
-                return {"error": f"send failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
-            return {"bytes": pool.packed_bytes(n), "blocks": n}
-        except Exception as e:  # data-path errors are reported, not raised
-            return {"error": f"NCCL send failed: {type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+        return self._staged_transfer(True, dst_rank, block_indices)
 
     def p2p_recv_kv(self, src_rank: int, block_indices: List[int]) -> Dict[str, Any]:
         """Receives chunk by chunk and scatters into `block_indices`."""
-        if not self.nccl_pg_initialized:
-            return {"error": "Global NCCL not initialized", "bytes": 0, "blocks": 0}
-        try:
-            pool = self._require_pool()
-            n = len(block_indices)
-            if n == 0:
-                return {"bytes": 0, "blocks": 0}
-            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices), unique=True))
-            chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
-            slots = self._staging_views(pool, n, chunks)
-            if self._nccl_comm is not None:
-                with _range("emm.p2p_recv_kv"):
-                    self._staging_views(pool, n, chunks)
-                    pool.recv_blocks(self._nccl_comm, src_rank, ids, self._staging, chunks[0][1])
-                torch.cuda.synchronize(self.device)
-                rc, detail = self.ctx.status()
-                if rc != _lib.OK:
-                    return {"error": f"recv failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
-                return {"bytes": pool.packed_bytes(n), "blocks": n}
-            main = torch.cuda.current_stream(self.device)
-            self._xfer_stream.wait_stream(main)
-            with torch.cuda.stream(self._xfer_stream), _range("emm.p2p_recv_kv"):
-                pipelined_recv(
-                    chunks, self._buffer_for(pool, n, slots),
-                    irecv=lambda buf: dist.irecv(pool._logical(buf), src=src_rank, group=self.process_group),
-                    unpack=lambda buf, b, c: pool.scatter(ids, buf, layer_begin=b, layer_count=c),
-                )
-            main.wait_stream(self._xfer_stream)
-            torch.cuda.synchronize(self.device)
-            rc, detail = self.ctx.status()
-            if rc != _lib.OK:
-                return {"error": f"recv failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
-            return {"bytes": pool.packed_bytes(n), "blocks": n}
-        except Exception as e:
-            return {"error": f"NCCL recv failed: {type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
+        return self._staged_transfer(False, src_rank, block_indices)
 
     def p2p_coordinated_transfer_kv(self, src_worker_ref: Any, src_rank: int, src_blocks: List[int],
                                     dst_blocks: List[int], timeout: float = 10.0) -> Dict[str, Any]:
