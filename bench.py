@@ -737,62 +737,6 @@ def bench_multi(args):
     dist.all_reduce(lt)
     value = payload * args.steps / (ms / 1e3) / 1e9
 
-    nccl_steps = max(2, args.steps // 4)
-    variants = {}
-    ms_p = max_ms(timed(step_push, nccl_steps, 2, device, barrier))
-    variants["peer_push"] = {"value": round(payload * nccl_steps / (ms_p / 1e3) / 1e9, 2), "unit": "GB/s",
-                             "ms_per_step": round(ms_p / nccl_steps, 3),
-                             "path": "sources store into the sinks' peer-mapped pools (same kernel, other direction)"}
-    try:
-        ms_n = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
-        variants["nccl_staged"] = {"value": round(payload * nccl_steps / (ms_n / 1e3) / 1e9, 2), "unit": "GB/s",
-                                   "ms_per_step": round(ms_n / nccl_steps, 3),
-                                   "path": "pack -> NCCL send/recv -> unpack, layer-chunk pipeline"}
-    except Exception as e:
-        variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
-
-    try:  # the same staged pipeline run inside the C library on its own communicator and streams
-        worker.init_native_nccl()
-        ms_nn = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
-        variants["nccl_staged_native"] = {"value": round(payload * nccl_steps / (ms_nn / 1e3) / 1e9, 2), "unit": "GB/s",
-                                          "ms_per_step": round(ms_nn / nccl_steps, 3),
-                                          "path": "emm_send_blocks / emm_recv_blocks: pack -> ncclSend, ncclRecv -> "
-                                                  "unpack on library streams"}
-        def step_a2a():
-            for plan in plans:
-                res = worker.migrate(plan, method="alltoall")
-                assert "error" not in res, res
-
-        ms_a = max_ms(timed(step_a2a, nccl_steps, 2, device, barrier))
-        variants["nccl_alltoall_pipelined"] = {
-            "value": round(payload * nccl_steps / (ms_a / 1e3) / 1e9, 2), "unit": "GB/s",
-            "ms_per_step": round(ms_a / nccl_steps, 3),
-            "path": "per layer chunk: one gather for all sinks, one grouped ncclSend/ncclRecv exchange among all "
-                    "ranks, one scatter for all sources; three streams, two staging slots"}
-    except Exception as e:
-        variants["nccl_staged_native"] = {"error": f"{type(e).__name__}: {e}"}
-
-    # Every rank a source and a sink at once (the rebalancing exchange): rank r loads the lower half of
-    # rank r+1's pool into the upper half of its own. Run last among the device-resident variants because
-    # it overwrites pool contents.
-    half = w["NB"] // 2
-    ring_src = worker.pool.upload_ids(torch.randperm(half, generator=torch.Generator().manual_seed(rank)).tolist())
-    ring_dst = worker.pool.upload_ids((torch.randperm(half, generator=torch.Generator().manual_seed(50 + rank)) + half).tolist())
-
-    def step_ring():
-        worker.peer_pools[nxt].copy_blocks(worker.pool, ring_src, ring_dst)
-        torch.cuda.synchronize(device)
-        dist.barrier()
-
-    ring_steps = max(3, args.steps // 2)
-    ms_r = max_ms(timed(step_ring, ring_steps, 2, device, barrier))
-    ring_bytes = world * half * block_bytes(w)
-    variants["ring_exchange_all_ranks"] = {
-        "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
-        "per_gpu_ingress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
-        "ms_per_step": round(ms_r / ring_steps, 3),
-        "path": "every rank pulls half of the next rank's pool into its own at the same time"}
-
     # end to end through the worker API with host id lists (tables uploaded inside the timed region)
     def step_e2e():
         for plan in plans:
@@ -803,6 +747,8 @@ def bench_multi(args):
     ms_e = max_ms(timed(step_e2e, e2e_steps, 2, device, barrier))
     h2d = sum(8 * len(t.src_blocks) for p in plans for t in p.transfers)
 
+    variants = {}
+    line = None
     if rank == 0:
         per_src_gbs = value / len(sources)
         line = {
@@ -832,7 +778,84 @@ def bench_multi(args):
             "clocks": clocks.summary(),
             "variants": variants,
         }
-        print(json.dumps(line))
+    def run_variants():
+        nccl_steps = max(2, args.steps // 4)
+        ms_p = max_ms(timed(step_push, nccl_steps, 2, device, barrier))
+        variants["peer_push"] = {"value": round(payload * nccl_steps / (ms_p / 1e3) / 1e9, 2), "unit": "GB/s",
+                                 "ms_per_step": round(ms_p / nccl_steps, 3),
+                                 "path": "sources store into the sinks' peer-mapped pools (same kernel, other direction)"}
+        try:
+            ms_n = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
+            variants["nccl_staged"] = {"value": round(payload * nccl_steps / (ms_n / 1e3) / 1e9, 2), "unit": "GB/s",
+                                       "ms_per_step": round(ms_n / nccl_steps, 3),
+                                       "path": "pack -> NCCL send/recv -> unpack, layer-chunk pipeline"}
+        except Exception as e:
+            variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
+
+        try:  # the same staged pipeline run inside the C library on its own communicator and streams
+            worker.init_native_nccl()
+            ms_nn = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
+            variants["nccl_staged_native"] = {"value": round(payload * nccl_steps / (ms_nn / 1e3) / 1e9, 2), "unit": "GB/s",
+                                              "ms_per_step": round(ms_nn / nccl_steps, 3),
+                                              "path": "emm_send_blocks / emm_recv_blocks: pack -> ncclSend, ncclRecv -> "
+                                                      "unpack on library streams"}
+            def step_a2a():
+                for plan in plans:
+                    res = worker.migrate(plan, method="alltoall")
+                    assert "error" not in res, res
+
+            ms_a = max_ms(timed(step_a2a, nccl_steps, 2, device, barrier))
+            variants["nccl_alltoall_pipelined"] = {
+                "value": round(payload * nccl_steps / (ms_a / 1e3) / 1e9, 2), "unit": "GB/s",
+                "ms_per_step": round(ms_a / nccl_steps, 3),
+                "path": "per layer chunk: one gather for all sinks, one grouped ncclSend/ncclRecv exchange among all "
+                        "ranks, one scatter for all sources; three streams, two staging slots"}
+        except Exception as e:
+            variants["nccl_staged_native"] = {"error": f"{type(e).__name__}: {e}"}
+
+        # Every rank a source and a sink at once (the rebalancing exchange): rank r loads the lower half of
+        # rank r+1's pool into the upper half of its own. Run last among the device-resident variants because
+        # it overwrites pool contents.
+        half = w["NB"] // 2
+        ring_src = worker.pool.upload_ids(torch.randperm(half, generator=torch.Generator().manual_seed(rank)).tolist())
+        ring_dst = worker.pool.upload_ids((torch.randperm(half, generator=torch.Generator().manual_seed(50 + rank)) + half).tolist())
+
+        def step_ring():
+            worker.peer_pools[nxt].copy_blocks(worker.pool, ring_src, ring_dst)
+            torch.cuda.synchronize(device)
+            dist.barrier()
+
+        ring_steps = max(3, args.steps // 2)
+        ms_r = max_ms(timed(step_ring, ring_steps, 2, device, barrier))
+        ring_bytes = world * half * block_bytes(w)
+        variants["ring_exchange_all_ranks"] = {
+            "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
+            "per_gpu_ingress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
+            "ms_per_step": round(ms_r / ring_steps, 3),
+            "path": "every rank pulls half of the next rank's pool into its own at the same time"}
+
+
+    # The variants are extras: if one of them stalls (an NCCL path on an unusual fabric), the headline
+    # line is still printed and the job ends instead of hanging until an outer limit kills it.
+    done = threading.Event()
+
+    def give_up():
+        if done.is_set():
+            return
+        if rank == 0:
+            variants["timed_out"] = True
+            print(json.dumps(line), flush=True)
+        os._exit(0)
+
+    watchdog = threading.Timer(float(os.environ.get("EMM_BENCH_VARIANT_LIMIT_S", "240")), give_up)
+    watchdog.daemon = True
+    watchdog.start()
+    if not args.skip_extras:
+        run_variants()
+    done.set()
+    watchdog.cancel()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
