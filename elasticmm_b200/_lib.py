@@ -120,6 +120,7 @@ SIGNATURES = {
     "emm_exchange": (C.c_int, [_P, C.c_int32, _I32P, C.POINTER(_P), C.POINTER(C.c_uint64), _I32P, _P]),
     "emm_send_blocks": (C.c_int, [_P, _P, C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_int32, _P]),
     "emm_recv_blocks": (C.c_int, [_P, _P, C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_int32, _P]),
+    "emm_enable_peer_access": (C.c_int, [_P, C.c_int]),
     "emm_ipc_export": (C.c_int, [_P, _P, C.c_char_p, C.POINTER(C.c_uint64)]),
     "emm_ipc_open": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.POINTER(_P)]),
 }

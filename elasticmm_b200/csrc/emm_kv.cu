@@ -975,6 +975,23 @@ int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES],
 }
 
 
+int emm_enable_peer_access(emm_ctx *ctx, int peer_device) {
+  if (!ctx) return fail(EMM_ERR_BAD_ARG, "enable_peer_access: null context");
+  if (peer_device == ctx->device) return EMM_OK;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  int can = 0;
+  EMM_CUDA(cudaDeviceCanAccessPeer(&can, ctx->device, peer_device));
+  if (!can) return fail(EMM_ERR_CUDA, "device %d cannot address device %d", ctx->device, peer_device);
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();  // clear the sticky "already enabled"
+    return EMM_OK;
+  }
+  if (e != cudaSuccess) return fail(EMM_ERR_CUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+  return EMM_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Staged transport over NCCL (entry points resolved with dlopen / dlsym)
 // ---------------------------------------------------------------------------

@@ -139,10 +139,14 @@ class V0KVTransferManager:
             elif self.peer_direction == "pull":
                 if dst is None:  # the sink does the copy; the source's half of the call is a no-op
                     return {"bytes": 0, "blocks": len(src_blocks), "passive": True}
+                if src is not None and src_rank not in dst.peer_pools:
+                    dst.attach_local_peer(src_rank, src)      # both workers in this process, two GPUs
                 worker, res = dst, dst.p2p_pull_kv(src_rank, src_blocks, dst_blocks)      # sink loads over the link
             else:
                 if src is None:
                     return {"bytes": 0, "blocks": len(src_blocks), "passive": True}
+                if dst is not None and dst_rank not in src.peer_pools:
+                    src.attach_local_peer(dst_rank, dst)
                 worker, res = src, src.p2p_push_kv(dst_rank, src_blocks, dst_blocks)      # source stores over the link
             if "error" not in res:
                 torch.cuda.synchronize(worker.device)

@@ -78,6 +78,7 @@ class V0Worker:
         self.swap_pool: Optional[KVPool] = None
         self.peer_pools: Dict[int, KVPool] = {}
         self._peer_streams: Dict[int, torch.cuda.Stream] = {}
+        self._peer_keepalive: Dict[int, Any] = {}
         self.ve_cache: Optional[Dict[str, torch.Tensor]] = None
         self.ve_blocks: Optional[torch.Tensor] = None
         self.ve_pool: Optional[KVPool] = None
@@ -468,6 +469,16 @@ class V0Worker:
         ptrs = [self.ctx.ipc_open(h, off) for h, off in handles]
         pd = _lib.PoolDesc(**desc)
         self.peer_pools[rank] = KVPool.from_pointers(self.ctx, pd, ptrs, dtype or self._require_pool().dtype)
+
+    def attach_local_peer(self, rank: int, worker: "V0Worker") -> None:
+        """Maps the pool of a worker that lives in THIS process on another GPU (one process
+        driving several GPUs): peer access is enabled and the same device pointers are used,
+        no IPC handle is needed."""
+        other = worker._require_pool()
+        self.ctx.enable_peer_access(worker.device)
+        desc = _lib.PoolDesc.from_buffer_copy(other.desc)
+        self.peer_pools[rank] = KVPool.from_pointers(self.ctx, desc, other.layer_ptrs, other.dtype)
+        self._peer_keepalive[rank] = worker  # the mapped memory belongs to that worker
 
     def p2p_push_kv(self, dst_rank: int, src_blocks: List[int], dst_blocks: List[int]) -> Dict[str, Any]:
         """Copies blocks straight into the mapped pool of `dst_rank`: one kernel,

@@ -105,6 +105,11 @@ class Context:
         _lib.check(self._lib.emm_ipc_open(self._h, handle, C.c_uint64(offset), C.byref(out)))
         return int(out.value)
 
+    def enable_peer_access(self, peer_device: Union[int, torch.device]) -> None:
+        """Lets this device's kernels address another GPU of the same process."""
+        index = peer_device if isinstance(peer_device, int) else torch.device(peer_device).index
+        _lib.check(self._lib.emm_enable_peer_access(self._h, int(index)))
+
     # -- NCCL communicator owned by the library ------------------------------------
     def nccl_unique_id(self) -> bytes:
         """A fresh NCCL unique id (rank 0 makes it and ships it to the other ranks)."""

@@ -320,6 +320,12 @@ int emm_ipc_export(emm_ctx *ctx, const void *d_ptr, unsigned char handle[EMM_IPC
 int emm_ipc_open(emm_ctx *ctx, const unsigned char handle[EMM_IPC_HANDLE_BYTES], uint64_t offset,
                  void **d_ptr);
 
+/* One process driving several GPUs: lets kernels of ctx's device address memory
+ * of `peer_device` directly (cudaDeviceEnablePeerAccess; already-enabled is not
+ * an error). A pool of the other GPU is then described to this context with
+ * emm_pool_create over the same device pointers; no IPC handle is involved. */
+int emm_enable_peer_access(emm_ctx *ctx, int peer_device);
+
 #ifdef __cplusplus
 }
 #endif

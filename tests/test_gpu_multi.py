@@ -298,3 +298,30 @@ def test_four_gpu_two_sources_two_sinks_is_bit_exact():
         for r in range(4):
             res = torch.load(os.path.join(d, f"r{r}.pt"))
             assert res and all(res.values()), f"rank {r}: {res}"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("direction", ["pull", "push"])
+def test_one_process_two_gpus(direction):
+    """One process driving two GPUs: the manager maps the other worker's pool by pointer and moves
+    the blocks with one direct kernel (loads or stores over NVLink); p2p_copy and staged_copy too."""
+    from elasticmm_b200.engine.v0 import TransferMethod, V0KVTransferManager, V0Worker
+    from oracle import kv_oracle
+
+    geom = dict(L=4, NB=64, BS=16, H=4, D=128)
+    src_cpu = kv_oracle.make_pool(geom["L"], geom["NB"], geom["BS"], geom["H"], geom["D"], torch.bfloat16, 5)
+    g = torch.Generator().manual_seed(1)
+    sperm, dperm = torch.randperm(geom["NB"], generator=g).tolist(), torch.randperm(geom["NB"], generator=g).tolist()
+    reqs = [(f"r{i}", sperm[i * 12:(i + 1) * 12], dperm[i * 12:(i + 1) * 12]) for i in range(3)]
+    for method in (TransferMethod.B200_PEER, TransferMethod.P2P_COPY, TransferMethod.STAGED_COPY):
+        dst_cpu = kv_oracle.make_pool(geom["L"], geom["NB"], geom["BS"], geom["H"], geom["D"], torch.bfloat16, 0,
+                                      fill="guard")
+        src = V0Worker(worker_id=0, dtype="bfloat16", device="cuda:0", kv_cache=[t.to("cuda:0") for t in src_cpu])
+        dst = V0Worker(worker_id=1, dtype="bfloat16", device="cuda:1", kv_cache=[t.to("cuda:1") for t in dst_cpu])
+        mgr = V0KVTransferManager(transfer_method=method, peer_direction=direction)
+        mgr.register_worker(0, src, "prefill")
+        mgr.register_worker(1, dst, "decoding")
+        for rid, s, d in reqs:
+            assert mgr.transfer_kv_cache_sync(rid, 0, 1, s, d), mgr.last_result
+            kv_oracle.write_kv_blocks(dst_cpu, d, kv_oracle.extract_kv_blocks(src_cpu, s))
+        assert all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(dst.kv_cache, dst_cpu)), method
