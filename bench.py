@@ -424,6 +424,8 @@ def bench_single(args):
         torch.cuda.empty_cache()
         extras["compaction"] = bench_compaction(ctx, device, args)
         torch.cuda.empty_cache()
+        extras["small_transfer"] = bench_small_transfer(ctx, device, args)
+        torch.cuda.empty_cache()
     cpu = cpu_baseline(wname) if not args.skip_cpu else None
     kernel_name = "page_copy_ldg" if ctx.get_option(_lib.OPT_COPY_VARIANT) == _lib.COPY_LDG else "page_copy_bulk"
 
@@ -543,6 +545,37 @@ def bench_append(ctx, device, args):
                                          "us_per_step": round(ms * 1e3 / steps, 2), "launches_per_step": L}
     except Exception as e:  # graph capture is a reporting extra, not part of the contract
         out["per_layer_graph_replay"] = {"error": f"{type(e).__name__}: {e}"}
+    return out
+
+
+def bench_small_transfer(ctx, device, args):
+    """Wall-clock cost of moving one short request through the manager API, device synchronised per
+    transfer as the reference's manager does: 15 blocks (a 234-token Qwen2.5-VL request, the example
+    size the reference's engine README quotes) between two pools on this GPU."""
+    from elasticmm_b200.engine.v0 import KVTransferMetrics, TransferMethod, V0KVTransferManager, V0Worker
+
+    w = dict(WORKLOADS["qwen25vl7b_cfg3"], NB=1024)
+    src = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 7))
+    dst = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 0, guard=True))
+    g = torch.Generator().manual_seed(7)
+    out = {"workload": "15 blocks of qwen25vl7b geometry (13.1 MiB payload)", "blocks": 15}
+    for name, method in (("p2p_copy", TransferMethod.P2P_COPY), ("b200_peer", TransferMethod.B200_PEER)):
+        metrics = KVTransferMetrics("decoding", block_bytes=src.pool.block_bytes())
+        mgr = V0KVTransferManager(transfer_method=method, metrics_callback=metrics.record_kv_transfer)
+        mgr.register_worker(0, src, "prefill")
+        mgr.register_worker(1, dst, "decoding")
+        n_iter = 300
+        tables = [(torch.randperm(w["NB"], generator=g)[:15].tolist(), torch.randperm(w["NB"], generator=g)[:15].tolist())
+                  for _ in range(n_iter)]
+        for s_ids, d_ids in tables[:20]:
+            mgr.transfer_kv_cache_sync("warm", 0, 1, s_ids, d_ids)
+        t0 = time.perf_counter()
+        for s_ids, d_ids in tables:
+            assert mgr.transfer_kv_cache_sync("r", 0, 1, s_ids, d_ids)
+        dt = time.perf_counter() - t0
+        out[name] = {"us_per_transfer": round(dt / n_iter * 1e6, 1), "blocks_per_s": round(15 * n_iter / dt),
+                     "payload_gbs": round(15 * src.pool.block_bytes() * n_iter / dt / 1e9, 1)}
+    out["gain_cost_params"] = {k: round(v, 7) for k, v in metrics.gain_cost_params().items()}
     return out
 
 
