@@ -410,12 +410,27 @@ def bench_single(args):
             src.copy_blocks(dst, s, d)
 
     ms_dw = timed(step_direct_waves, direct_steps, 3, device)
+    # gather -> per-request packed buffers -> scatter with one launch per wave for each direction
+    many, pos = [], 0
+    for wave in waves:
+        s_lists = [reqs[pos + k][0] for k in range(len(wave))]
+        d_lists = [reqs[pos + k][1] for k in range(len(wave))]
+        many.append((src.many_tables(s_lists), dst.many_tables(d_lists, unique=True)))
+        pos += len(wave)
+    many_flat = torch.empty(max(src.packed_bytes(t[0][1]) for t in many) // 2, dtype=src.dtype, device=device)
+
+    def step_many():
+        for s_tab, d_tab in many:
+            src.gather_many_into(s_tab, many_flat)
+            dst.scatter_many_from(d_tab, many_flat)
+
+    ms_many = timed(step_many, direct_steps, 3, device)
     ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3, device)
     e2e_steps = max(3, args.steps // 4)
     e2e_value = payload * e2e_steps / (ms_e2e / 1e3) / 1e9
     h2d = sum(4 * (len(s) + len(d)) for s, d in reqs)
 
-    del packed, flat, dev_tables, wave_tables
+    del packed, flat, dev_tables, wave_tables, many, many_flat
     extras = {}
     if not args.skip_extras:
         src_worker = dst_worker = src = dst = None
@@ -460,7 +475,13 @@ def bench_single(args):
                 "value": round(payload * direct_steps / (ms_dw / 1e3) / 1e9, 2), "unit": "GB/s",
                 "hbm_gbs": round(2 * payload * direct_steps / (ms_dw / 1e3) / 1e9, 1),
                 "ms_per_step": round(ms_dw / direct_steps, 3), "launches_per_step": len(waves),
-                "path": "the same copies with one launch per wave over concatenated tables (plan-level batching)"}},
+                "path": "the same copies with one launch per wave over concatenated tables (plan-level batching)"},
+            "gather_scatter_many_per_wave": {
+                "value": round(payload * direct_steps / (ms_many / 1e3) / 1e9, 2), "unit": "GB/s",
+                "hbm_gbs": round(4 * payload * direct_steps / (ms_many / 1e3) / 1e9, 1),
+                "ms_per_step": round(ms_many / direct_steps, 3), "launches_per_step": 2 * len(waves),
+                "path": "gather into one contiguous buffer per request, then scatter, all requests of a wave in one "
+                        "launch per direction (emm_gather_many / emm_scatter_many)"}},
     }
     line.update(extras)
     print(json.dumps(line))

@@ -101,6 +101,8 @@ SIGNATURES = {
     "emm_scatter": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_gather_layers": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_scatter_layers": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_uint64, _P]),
+    "emm_gather_many": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
+    "emm_scatter_many": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
     "emm_copy_blocks": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P]),
     "emm_gather_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_scatter_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),

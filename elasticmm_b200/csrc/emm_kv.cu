@@ -220,6 +220,9 @@ CopySide pool_side(const emm_pool *p, const int32_t *ids) {
   s.block_stride = (uint64_t)p->desc.block_stride;
   s.ids = ids;
   s.num_blocks = (uint32_t)p->desc.num_blocks;
+  s.seg_prefix = nullptr;
+  s.num_segs = 0;
+  s.seg_stride = 0;
   return s;
 }
 
@@ -233,18 +236,30 @@ CopySide packed_side(const void *packed, int32_t n, int64_t page, int planes = 2
   s.block_stride = (uint64_t)page;
   s.ids = nullptr;
   s.num_blocks = (uint32_t)n;
+  s.seg_prefix = nullptr;
+  s.num_segs = 0;
+  s.seg_stride = 0;
   return s;
 }
 
-template <typename V>
+template <typename V, bool kSeg>
 int launch_ldg_typed(emm_ctx *ctx, const PageCopyArgs &a, int grid, cudaStream_t st) {
   switch (ctx->ldg_unroll) {
-    case 1: emm::page_copy_ldg<V, 1><<<grid, 256, 0, st>>>(a); break;
-    case 2: emm::page_copy_ldg<V, 2><<<grid, 256, 0, st>>>(a); break;
-    case 8: emm::page_copy_ldg<V, 8><<<grid, 256, 0, st>>>(a); break;
-    default: emm::page_copy_ldg<V, 4><<<grid, 256, 0, st>>>(a); break;
+    case 1: emm::page_copy_ldg<V, 1, kSeg><<<grid, 256, 0, st>>>(a); break;
+    case 2: emm::page_copy_ldg<V, 2, kSeg><<<grid, 256, 0, st>>>(a); break;
+    case 8: emm::page_copy_ldg<V, 8, kSeg><<<grid, 256, 0, st>>>(a); break;
+    default: emm::page_copy_ldg<V, 4, kSeg><<<grid, 256, 0, st>>>(a); break;
   }
   return EMM_OK;
+}
+
+template <bool kSeg>
+void launch_ldg(emm_ctx *ctx, const PageCopyArgs &a, int grid, uint32_t align, cudaStream_t st) {
+  if (align >= 16) launch_ldg_typed<uint4, kSeg>(ctx, a, grid, st);
+  else if (align >= 8) launch_ldg_typed<uint2, kSeg>(ctx, a, grid, st);
+  else if (align >= 4) launch_ldg_typed<uint32_t, kSeg>(ctx, a, grid, st);
+  else if (align >= 2) launch_ldg_typed<uint16_t, kSeg>(ctx, a, grid, st);
+  else launch_ldg_typed<uint8_t, kSeg>(ctx, a, grid, st);
 }
 
 // Launches the page copy described by (src, dst). `align` is the common
@@ -271,6 +286,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   a.layer_count = (uint32_t)layer_count;
   a.page_bytes = (uint32_t)page_bytes;
   a.status = ctx->d_status;
+  const bool segmented = src.seg_prefix != nullptr || dst.seg_prefix != nullptr;
 
   int64_t chunk = ctx->chunk_bytes;
   if (chunk <= 0) chunk = (variant == EMM_COPY_BULK) ? 32768 : 65536;
@@ -304,7 +320,9 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   if (variant == EMM_COPY_BULK) {
     const int smem = (int)((int64_t)warps * ctx->stages * chunk);
     if (smem > ctx->bulk_smem_set) {
-      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk,
+      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<false>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<true>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       ctx->bulk_smem_set = smem;
     }
@@ -315,7 +333,10 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(want, cap);
-    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
+    if (segmented)
+      emm::page_copy_bulk<true><<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
+    else
+      emm::page_copy_bulk<false><<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
   } else {
     // A copy to or from a peer GPU or pinned host memory is bound by the link, not
     // by HBM: 48 CTAs already saturate NVLink (measured), and side-by-side copies
@@ -325,11 +346,8 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(a.total_chunks, cap);
-    if (align >= 16) launch_ldg_typed<uint4>(ctx, a, grid, st);
-    else if (align >= 8) launch_ldg_typed<uint2>(ctx, a, grid, st);
-    else if (align >= 4) launch_ldg_typed<uint32_t>(ctx, a, grid, st);
-    else if (align >= 2) launch_ldg_typed<uint16_t>(ctx, a, grid, st);
-    else launch_ldg_typed<uint8_t>(ctx, a, grid, st);
+    if (segmented) launch_ldg<true>(ctx, a, grid, align, st);
+    else launch_ldg<false>(ctx, a, grid, align, st);
   }
   EMM_CUDA(cudaGetLastError());
   ctx->launches += 1;
@@ -352,7 +370,7 @@ int check_layer_range(const emm_pool *p, int32_t begin, int32_t count) {
 
 int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t layer_count,
                 const int32_t *d_ids, int32_t n, const void *d_packed, uint64_t packed_bytes,
-                void *stream) {
+                void *stream, const uint32_t *d_seg_prefix = nullptr, int32_t num_segs = 0) {
   const char *what = to_packed ? "gather" : "scatter";
   if (int rc = check_pool_for_pages(pool, what)) return rc;
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
@@ -368,6 +386,11 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
     return fail(EMM_ERR_ALIGN, "%s: packed buffer not aligned to elem_size", what);
   CopySide ps = pool_side(pool, d_ids);
   CopySide bs = packed_side(d_packed, n, pool->page_bytes, pool->planes);
+  if (d_seg_prefix) {
+    bs.seg_prefix = d_seg_prefix;
+    bs.num_segs = (uint32_t)num_segs;
+    bs.seg_stride = (uint64_t)layer_count * (uint64_t)pool->planes * (uint64_t)pool->page_bytes;
+  }
   return to_packed ? launch_page_copy(pool->ctx, ps, bs, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
                                       (cudaStream_t)stream, pool->planes)
@@ -703,6 +726,27 @@ int emm_scatter_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
                        uint64_t packed_bytes, void *stream) {
   if (!pool) return fail(EMM_ERR_BAD_ARG, "scatter: null pool");
   return packed_copy(pool, false, layer_begin, layer_count, d_ids, n, d_packed, packed_bytes, stream);
+}
+
+static int many_impl(emm_pool *pool, bool to_packed, const int32_t *d_ids, const uint32_t *d_seg_prefix,
+                     int32_t num_segs, int32_t n_total, const void *d_packed, uint64_t packed_bytes,
+                     void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: null pool");
+  if (num_segs < 0 || n_total < 0) return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: negative count");
+  if (n_total > 0 && (num_segs == 0 || !d_seg_prefix))
+    return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: blocks without segments");
+  return packed_copy(pool, to_packed, 0, pool->desc.num_layers, d_ids, n_total, d_packed, packed_bytes, stream,
+                     d_seg_prefix, num_segs);
+}
+
+int emm_gather_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
+                    int32_t n_total, void *d_packed, uint64_t packed_bytes, void *stream) {
+  return many_impl(pool, true, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
+}
+
+int emm_scatter_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
+                     int32_t n_total, const void *d_packed, uint64_t packed_bytes, void *stream) {
+  return many_impl(pool, false, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
 }
 
 int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
@@ -1339,6 +1383,9 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   a.src.block_stride = (uint64_t)desc->block_stride;
   a.src.ids = reinterpret_cast<const int32_t *>(d_ids);
   a.src.num_blocks = (uint32_t)desc->num_blocks;
+  a.src.seg_prefix = nullptr;
+  a.src.num_segs = 0;
+  a.src.seg_stride = 0;
   a.dst = packed_side(d_packed, n, page, planes);
   a.n = (uint32_t)n;
   a.plane_shift = planes == 2 ? 1u : 0u;
@@ -1361,22 +1408,22 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     if (smem > nd->max_smem_optin - 2048)
       return fail(EMM_ERR_BAD_ARG, "gather_noalloc: ring does not fit shared memory");
     if (smem > nd->smem_set) {
-      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       nd->smem_set = smem;
     }
     const uint64_t want_ctas = (a.total_chunks + warps - 1) / warps;
     const int grid = (int)std::min<uint64_t>(want_ctas, (uint64_t)nd->sm_count * per_sm);
-    emm::page_copy_bulk<<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages, 0u);
+    emm::page_copy_bulk<false><<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages, 0u);
   } else {
     int64_t chunk = std::min<int64_t>(65536, page);
     a.chunk_bytes = (uint32_t)chunk;
     a.chunks_per_page = (uint32_t)((page + chunk - 1) / chunk);
     a.total_chunks = (uint64_t)desc->num_layers * (uint64_t)planes * (uint64_t)n * a.chunks_per_page;
     const int grid = (int)std::min<uint64_t>(a.total_chunks, (uint64_t)nd->sm_count * 4);
-    if (align >= 8) emm::page_copy_ldg<uint2, 2><<<grid, 256, 0, st>>>(a);
-    else if (align >= 4) emm::page_copy_ldg<uint32_t, 2><<<grid, 256, 0, st>>>(a);
-    else if (align >= 2) emm::page_copy_ldg<uint16_t, 2><<<grid, 256, 0, st>>>(a);
-    else emm::page_copy_ldg<uint8_t, 2><<<grid, 256, 0, st>>>(a);
+    if (align >= 8) emm::page_copy_ldg<uint2, 2, false><<<grid, 256, 0, st>>>(a);
+    else if (align >= 4) emm::page_copy_ldg<uint32_t, 2, false><<<grid, 256, 0, st>>>(a);
+    else if (align >= 2) emm::page_copy_ldg<uint16_t, 2, false><<<grid, 256, 0, st>>>(a);
+    else emm::page_copy_ldg<uint8_t, 2, false><<<grid, 256, 0, st>>>(a);
   }
   EMM_CUDA(cudaGetLastError());
   return EMM_OK;

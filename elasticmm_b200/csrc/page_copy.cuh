@@ -41,6 +41,11 @@ struct CopySide {
   uint64_t block_stride;
   const int32_t *ids;      // device table of n ids, or nullptr for identity
   uint32_t num_blocks;     // bound for ids (ignored for identity)
+  // Segmented packed side (several requests, each with its own [layers, planes, n_r, page]
+  // buffer laid end to end): prefix sums of the requests' block counts, or nullptr.
+  const uint32_t *seg_prefix;  // device array of num_segs + 1 entries, seg_prefix[0] == 0
+  uint32_t num_segs;
+  uint64_t seg_stride;         // bytes one block occupies over the moved layers and planes
 };
 
 struct PageCopyArgs {
@@ -78,8 +83,26 @@ __device__ __forceinline__ void report(int *status, int code, long long detail) 
   }
 }
 
+// Address of page (lrel, p, i) on a segmented packed side: request r with
+// seg_prefix[r] <= i < seg_prefix[r+1] owns a [layers, planes, n_r, page] buffer that
+// starts seg_prefix[r] * seg_stride bytes into the allocation.
+__device__ __forceinline__ uint64_t segmented_address(const CopySide &sd, uint32_t i, uint32_t lrel,
+                                                      uint32_t p, uint32_t planes) {
+  uint32_t lo = 0, hi = sd.num_segs;
+  while (hi - lo > 1) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (sd.seg_prefix[mid] <= i) lo = mid;
+    else hi = mid;
+  }
+  const uint32_t start = sd.seg_prefix[lo];
+  const uint32_t n_r = sd.seg_prefix[lo + 1] - start;
+  return sd.base + (uint64_t)start * sd.seg_stride +
+         ((uint64_t)(lrel * planes + p) * n_r + (i - start)) * sd.block_stride;
+}
+
 // Decodes chunk g into addresses. Uniform across the threads that call it
 // with the same g (table and layer-pointer reads are broadcasts).
+template <bool kSeg>
 __device__ __forceinline__ ChunkAddr decode_chunk(const PageCopyArgs &a, uint64_t g) {
   uint64_t page = g / a.chunks_per_page;
   uint32_t c = (uint32_t)(g - page * a.chunks_per_page);
@@ -106,10 +129,20 @@ __device__ __forceinline__ ChunkAddr decode_chunk(const PageCopyArgs &a, uint64_
     r.dst = 0;
     return r;
   }
-  uint64_t sbase = a.src.layers ? a.src.layers[l] : a.src.base + (uint64_t)lrel * a.src.layer_stride;
-  uint64_t dbase = a.dst.layers ? a.dst.layers[l] : a.dst.base + (uint64_t)lrel * a.dst.layer_stride;
-  r.src = sbase + (uint64_t)p * a.src.plane_stride + (uint64_t)(uint32_t)sid * a.src.block_stride + off;
-  r.dst = dbase + (uint64_t)p * a.dst.plane_stride + (uint64_t)(uint32_t)did * a.dst.block_stride + off;
+  // kSeg kernels serve the several-requests-per-launch entries: the packed side (the one without
+  // a layer-pointer array) is then addressed through the segment table.
+  if (kSeg && a.src.seg_prefix) {
+    r.src = segmented_address(a.src, i, lrel, p, a.plane_shift + 1u) + off;
+  } else {
+    const uint64_t sbase = a.src.layers ? a.src.layers[l] : a.src.base + (uint64_t)lrel * a.src.layer_stride;
+    r.src = sbase + (uint64_t)p * a.src.plane_stride + (uint64_t)(uint32_t)sid * a.src.block_stride + off;
+  }
+  if (kSeg && a.dst.seg_prefix) {
+    r.dst = segmented_address(a.dst, i, lrel, p, a.plane_shift + 1u) + off;
+  } else {
+    const uint64_t dbase = a.dst.layers ? a.dst.layers[l] : a.dst.base + (uint64_t)lrel * a.dst.layer_stride;
+    r.dst = dbase + (uint64_t)p * a.dst.plane_stride + (uint64_t)(uint32_t)did * a.dst.block_stride + off;
+  }
   return r;
 }
 
@@ -231,6 +264,7 @@ __device__ __forceinline__ void bulk_wait_all() {
 // issues store j, then waits until store j-1 has finished reading its slot and
 // refills that slot with load j+stages-1. Addresses for the next load are
 // decoded one iteration early so the table read is off the critical path.
+template <bool kSeg>
 __global__ void __launch_bounds__(kMaxWarps * 32)
 page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hint) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
@@ -273,13 +307,13 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
 
   const uint64_t prologue = n_mine < (uint64_t)(stages - 1) ? n_mine : (uint64_t)(stages - 1);
   for (uint64_t j = 0; j < prologue; ++j)
-    issue(decode_chunk(a, stream_id + j * stream_step), (uint32_t)j);
+    issue(decode_chunk<kSeg>(a, stream_id + j * stream_step), (uint32_t)j);
 
   uint64_t jn = prologue;  // next chunk of this stream to load
   ChunkAddr next_ca;
   next_ca.src = next_ca.dst = 0;
   next_ca.len = 0;
-  if (jn < n_mine) next_ca = decode_chunk(a, stream_id + jn * stream_step);
+  if (jn < n_mine) next_ca = decode_chunk<kSeg>(a, stream_id + jn * stream_step);
 
   bool timed_out = false;
   uint32_t s = 0;       // slot of chunk j
@@ -288,7 +322,7 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
   for (; j < n_mine; ++j) {
     // Decode one load ahead: these global reads complete while we wait below.
     const ChunkAddr cur_ca = next_ca;
-    if (jn + 1 < n_mine) next_ca = decode_chunk(a, stream_id + (jn + 1) * stream_step);
+    if (jn + 1 < n_mine) next_ca = decode_chunk<kSeg>(a, stream_id + (jn + 1) * stream_step);
 
     if (!mbar_wait_bounded(smem_u32(&my_bars[s]), parity)) {
       report(a.status, kStatusTimeout, (long long)(stream_id + j * stream_step));
@@ -356,10 +390,10 @@ __device__ __forceinline__ void store_stream<uint4>(uint4 *p, const uint4 &v) {
 
 // One CTA per chunk, grid-stride. Each thread moves up to U vectors of type V
 // per pass; all U loads are issued before the first store.
-template <typename V, int U>
+template <typename V, int U, bool kSeg>
 __global__ void __launch_bounds__(256) page_copy_ldg(const PageCopyArgs a) {
   for (uint64_t g = blockIdx.x; g < a.total_chunks; g += gridDim.x) {
-    const ChunkAddr ca = decode_chunk(a, g);
+    const ChunkAddr ca = decode_chunk<kSeg>(a, g);
     if (ca.len == 0) continue;
     const V *__restrict__ sp = reinterpret_cast<const V *>(ca.src);
     V *__restrict__ dp = reinterpret_cast<V *>(ca.dst);

@@ -150,6 +150,19 @@ class V0Worker:
         with _range("emm.write_kv_blocks"):
             pool.scatter(block_indices, kv_data)
 
+    def extract_kv_blocks_many(self, block_index_lists: Sequence[List[int]]) -> List[torch.Tensor]:
+        """extract_kv_blocks for several requests with one kernel launch; one tensor per request."""
+        with _range("emm.extract_kv_blocks_many"):
+            return self._require_pool().gather_many(block_index_lists)
+
+    def write_kv_blocks_many(self, block_index_lists: Sequence[List[int]], kv_data: Sequence[torch.Tensor]) -> None:
+        """write_kv_blocks for several requests with one launch; `kv_data` as returned by
+        extract_kv_blocks_many (possibly of another worker on the same GPU)."""
+        for ids, data in zip(block_index_lists, kv_data):
+            assert data.shape[2] == len(ids), f"Block count mismatch: {data.shape[2]} vs {len(ids)}"
+        with _range("emm.write_kv_blocks_many"):
+            self._require_pool().scatter_many(block_index_lists, kv_data)
+
     def get_kv_cache_layout(self) -> Dict[str, Any]:
         if not self.kv_cache:
             return {}

@@ -371,6 +371,97 @@ class KVPool:
         ptr, nbytes = self._packed_ptr(packed, n, lc)
         _lib.check(lib.emm_scatter_h(self._h, host.ctypes.data_as(C.c_void_p), n, C.c_void_p(ptr), nbytes, st))
 
+    # -- several requests per launch ---------------------------------------------------
+    def _many_tables(self, id_lists: Sequence[IdList], unique: bool):
+        hosts = [_as_host_ids(x) for x in id_lists]
+        counts = [h.shape[0] for h in hosts]
+        flat = np.concatenate(hosts) if hosts else np.empty(0, dtype=np.int64)
+        self._validated(flat, unique=unique)
+        prefix = np.zeros(len(counts) + 1, dtype=np.int64)
+        np.cumsum(counts, out=prefix[1:])
+        both = torch.from_numpy(np.concatenate([flat, prefix]).astype(np.int32)).pin_memory()
+        dev = both.to(self.device, non_blocking=True)
+        return counts, int(prefix[-1]), dev[: flat.shape[0]], dev[flat.shape[0]:]
+
+    def gather_many(self, id_lists: Sequence[IdList]) -> List[torch.Tensor]:
+        """extract_kv_blocks for several requests in one launch.
+
+        Returns one tensor [L, 2, n_r, BS, H, D] per request; they are views of a
+        single allocation in which the requests' buffers lie end to end.
+        """
+        counts, total, ids, prefix = self._many_tables(id_lists, unique=False)
+        flat = torch.empty(self.packed_bytes(total) // self.elem_size, dtype=self.dtype, device=self.device)
+        if total:
+            _lib.check(self.ctx._lib.emm_gather_many(
+                self._h, C.c_void_p(ids.data_ptr()), C.c_void_p(prefix.data_ptr()), len(counts), total,
+                C.c_void_p(flat.data_ptr()), flat.numel() * self.elem_size, C.c_void_p(_stream_ptr(self.device))))
+        return self._split_many(flat, counts)
+
+    def many_tables(self, id_lists: Sequence[IdList], unique: bool = False):
+        """Uploads the tables of several requests once: (counts, n_total, ids, prefix), for
+        gather_many_into / scatter_many_from when the same tables are used repeatedly."""
+        return self._many_tables(id_lists, unique)
+
+    def gather_many_into(self, tables, flat: torch.Tensor) -> List[torch.Tensor]:
+        """gather_many with tables from many_tables and a caller-owned flat buffer."""
+        counts, total, ids, prefix = tables
+        nbytes = self.packed_bytes(total)
+        if flat.numel() * flat.element_size() < nbytes or flat.dtype != self.dtype or not flat.is_contiguous():
+            raise ValueError("flat buffer too small, of another dtype, or not contiguous")
+        if total:
+            _lib.check(self.ctx._lib.emm_gather_many(
+                self._h, C.c_void_p(ids.data_ptr()), C.c_void_p(prefix.data_ptr()), len(counts), total,
+                C.c_void_p(flat.data_ptr()), nbytes, C.c_void_p(_stream_ptr(self.device))))
+        return self._split_many(flat, counts)
+
+    def scatter_many_from(self, tables, flat: torch.Tensor) -> None:
+        """scatter_many with tables from many_tables and the flat buffer gather_many_into filled."""
+        counts, total, ids, prefix = tables
+        nbytes = self.packed_bytes(total)
+        if flat.numel() * flat.element_size() < nbytes or flat.dtype != self.dtype or not flat.is_contiguous():
+            raise ValueError("flat buffer too small, of another dtype, or not contiguous")
+        if total:
+            _lib.check(self.ctx._lib.emm_scatter_many(
+                self._h, C.c_void_p(ids.data_ptr()), C.c_void_p(prefix.data_ptr()), len(counts), total,
+                C.c_void_p(flat.data_ptr()), nbytes, C.c_void_p(_stream_ptr(self.device))))
+
+    def _split_many(self, flat: torch.Tensor, counts: Sequence[int]) -> List[torch.Tensor]:
+        out, pos = [], 0
+        per_block = self.packed_bytes(1) // self.elem_size
+        for n in counts:
+            piece = flat[pos: pos + n * per_block]
+            out.append(self._logical(piece.view(self.packed_shape(n))))
+            pos += n * per_block
+        return out
+
+    def scatter_many(self, id_lists: Sequence[IdList], packed: Union[torch.Tensor, Sequence[torch.Tensor]]) -> None:
+        """write_kv_blocks for several requests in one launch.
+
+        `packed` is the list gather_many returned (buffers end to end in one
+        allocation) or that allocation as one flat tensor.
+        """
+        counts, total, ids, prefix = self._many_tables(id_lists, unique=True)
+        if isinstance(packed, torch.Tensor):
+            flat = packed.reshape(-1)
+        else:
+            pieces = [self._logical(t) for t in packed]
+            if [t.shape[2] for t in packed] != list(counts):
+                raise ValueError("packed buffers do not match the block counts of the id lists")
+            filled = [t for t in pieces if t.numel()]
+            pos = 0
+            for t in filled:  # the buffers must lie end to end, as gather_many lays them out
+                if not t.is_contiguous() or t.data_ptr() != filled[0].data_ptr() + pos:
+                    raise ValueError("packed buffers must be contiguous and adjacent (use gather_many's result)")
+                if t.dtype != self.dtype or t.device != self.device:
+                    raise ValueError("packed buffers must have the pool's dtype and device")
+                pos += t.numel() * t.element_size()
+            flat = filled[0] if filled else torch.empty(0, dtype=self.dtype, device=self.device)
+        nbytes = self.packed_bytes(total)
+        if total:
+            _lib.check(self.ctx._lib.emm_scatter_many(
+                self._h, C.c_void_p(ids.data_ptr()), C.c_void_p(prefix.data_ptr()), len(counts), total,
+                C.c_void_p(flat.data_ptr()), nbytes, C.c_void_p(_stream_ptr(self.device))))
+
     def _validated(self, host: np.ndarray, unique: bool = False) -> np.ndarray:
         if host.size and (host.min() < 0 or host.max() >= self.num_blocks):
             raise _lib.EmmError(_lib.ERR_ID_RANGE, f"block id outside [0, {self.num_blocks})")

@@ -178,6 +178,20 @@ int emm_scatter_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
                        const int32_t *d_ids, int32_t n, const void *d_packed,
                        uint64_t packed_bytes, void *stream);
 
+/* Several requests in one launch, each with its own packed buffer. `d_ids`
+ * holds the requests' tables one after the other (n_total ids),
+ * `d_seg_prefix` is a DEVICE array of num_segs + 1 prefix sums of their block
+ * counts (first entry 0, last n_total). Request r's buffer [L, 2, n_r, page]
+ * starts L*2*page*seg_prefix[r] bytes into `d_packed`, so the buffers lie end
+ * to end and `packed_bytes` is L*2*n_total*page. One launch instead of one per
+ * request is what the reference's batching branch aims at when it merges the
+ * transfers of a worker pair (elasticmm/engine/v0/kv_transfer.py:342-418),
+ * here without giving up one contiguous tensor per request. */
+int emm_gather_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
+                    int32_t n_total, void *d_packed, uint64_t packed_bytes, void *stream);
+int emm_scatter_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
+                     int32_t n_total, const void *d_packed, uint64_t packed_bytes, void *stream);
+
 /* Block copy: dst[l][p][dst_ids[i]] = src[l][p][src_ids[i]] with no staging
  * buffer. src and dst may be the same pool (compaction; id sets must not
  * overlap), two pools on one GPU, a pool in pinned host memory (swap), or a

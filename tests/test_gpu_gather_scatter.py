@@ -202,3 +202,41 @@ def test_device_table_entries_replay_from_a_cuda_graph(ctx):
         kv_oracle.write_kv_blocks(dst_cpu, d_ids, kv_oracle.extract_kv_blocks(src_cpu, s_ids))
     assert_clean(ctx)
     assert pools_equal(dst.layers, dst_cpu)
+
+
+@pytest.mark.parametrize("opts", [BULK_DEFAULT, LDG_DEFAULT], ids=vid)
+@pytest.mark.parametrize("case", [cases.KV_CASES[0], cases.KV_CASES[4], cases.KV_CASES[10]], ids=lambda c: c["name"])
+def test_many_requests_in_one_launch(ctx, opts, case):
+    """gather_many / scatter_many: one launch, one contiguous tensor per request, same bytes as the
+    per-request calls (and as the reference's per-request functions)."""
+    from elasticmm_b200.engine.v0 import V0Worker
+
+    configure(ctx, **opts)
+    src_cpu, dst_cpu = cases.build_pools(case)
+    src = V0Worker(dtype=case["dtype"], device="cuda:0", kv_cache=to_gpu(src_cpu))
+    dst = V0Worker(dtype=case["dtype"], device="cuda:0", kv_cache=to_gpu(dst_cpu))
+    g = torch.Generator().manual_seed(3)
+    sperm = torch.randperm(case["NB"], generator=g).tolist()
+    dperm = torch.randperm(case["dst_NB"], generator=g).tolist()
+    sizes, pos, s_lists, d_lists = [], 0, [], []
+    while pos < min(case["NB"], case["dst_NB"]):
+        n = min(int(torch.randint(0, 6, (1,), generator=g)), min(case["NB"], case["dst_NB"]) - pos)
+        s_lists.append(sperm[pos:pos + n])
+        d_lists.append(dperm[pos:pos + n])
+        pos += max(n, 1) if n else 1
+    before = ctx.launch_count
+    parts = src.extract_kv_blocks_many(s_lists)
+    assert ctx.launch_count - before == 1 and len(parts) == len(s_lists)
+    for ids, part in zip(s_lists, parts):
+        assert part.shape[2] == len(ids)
+        assert kv_oracle.bit_equal(part.cpu(), kv_oracle.extract_kv_blocks(src_cpu, ids))
+    dst.write_kv_blocks_many(d_lists, parts)
+    assert ctx.launch_count - before == 2
+    for ids, d_ids in zip(s_lists, d_lists):
+        kv_oracle.write_kv_blocks(dst_cpu, d_ids, kv_oracle.extract_kv_blocks(src_cpu, ids))
+    assert_clean(ctx)
+    assert pools_equal(dst.kv_cache, dst_cpu)
+    with pytest.raises(EmmError):
+        src.extract_kv_blocks_many([[0], [case["NB"]]])
+    with pytest.raises(EmmError):
+        dst.write_kv_blocks_many([[1], [1]], src.extract_kv_blocks_many([[0], [1]]))
