@@ -191,7 +191,16 @@ class V0KVTransferManager:
             dst_all = [b for _, _, d in queued for b in d]
             start = time.perf_counter()
             try:
-                res = self._run(key[0], key[1], src_all, dst_all)
+                src, dst = self.worker_registry.get(key[0]), self.worker_registry.get(key[1])
+                if (self.transfer_method == TransferMethod.P2P_COPY and src is not None and dst is not None
+                        and src.device == dst.device and hasattr(src, "extract_kv_blocks_many")):
+                    # one launch per direction, one contiguous tensor per request
+                    parts = src.extract_kv_blocks_many([s for _, s, _ in queued])
+                    dst.write_kv_blocks_many([d for _, _, d in queued], parts)
+                    torch.cuda.synchronize(dst.device)
+                    res = {"bytes": sum(t.numel() * t.element_size() for t in parts), "blocks": len(src_all)}
+                else:
+                    res = self._run(key[0], key[1], src_all, dst_all)
             except Exception as e:
                 res = {"error": f"{type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
             self.last_result = res
@@ -203,7 +212,7 @@ class V0KVTransferManager:
 
     def transfer_kv_cache_sync(self, request_id: str, src_rank: int, dst_rank: int,
                                src_blocks: List[int], dst_blocks: List[int]) -> bool:
-        if self.enable_batching and self.transfer_method != TransferMethod.P2P_COPY:
+        if self.enable_batching:
             # Merge small transfers of the same pair (the intent of the reference's batching branch,
             # elasticmm/engine/v0/kv_transfer.py:342-418,437-465): queue, and flush once `batch_size`
             # requests wait or `batch_timeout` has passed since the pair's last flush.

@@ -135,3 +135,27 @@ def test_reshape_and_cache_via_worker_and_block_manager_slots():
     w2, cpu2 = make_worker(8)
     w2.reshape_and_cache_all_layers(key.cuda(), value.cuda(), slots_t.cuda())
     assert pools_equal(w2.kv_cache, cpu)
+
+
+@pytest.mark.parametrize("method", [TransferMethod.P2P_COPY, TransferMethod.B200_PEER])
+def test_manager_batching_on_gpu(method):
+    """enable_batching: queued requests of a pair move together (one launch per direction for
+    p2p_copy, one merged direct copy for b200_peer) and land exactly where the serial calls put them."""
+    src, src_cpu = make_worker(3)
+    dst, dst_cpu = make_worker(0, guard=True)
+    mgr = V0KVTransferManager(transfer_method=method, enable_batching=True, batch_size=4, batch_timeout=3600.0)
+    mgr.register_worker(0, src, "prefill")
+    mgr.register_worker(1, dst, "decoding")
+    g = torch.Generator().manual_seed(6)
+    sperm, dperm = torch.randperm(64, generator=g).tolist(), torch.randperm(64, generator=g).tolist()
+    pos = 0
+    launches = src.ctx.launch_count
+    for i, n in enumerate([5, 1, 9, 3, 7, 2]):
+        s, d = sperm[pos:pos + n], dperm[pos:pos + n]
+        assert asyncio.run(mgr.transfer_kv_cache(f"r{i}", 0, 1, s, d))
+        kv_oracle.write_kv_blocks(dst_cpu, d, kv_oracle.extract_kv_blocks(src_cpu, s))
+        pos += n
+    assert src.ctx.launch_count - launches == (2 if method == TransferMethod.P2P_COPY else 1)  # first four flushed
+    assert mgr.flush()                                                                          # the last two
+    assert src.ctx.launch_count - launches == (4 if method == TransferMethod.P2P_COPY else 2)
+    assert pools_equal(dst.kv_cache, dst_cpu)
