@@ -65,6 +65,15 @@ class V0KVTransferManager:
         self._batch_flush_threshold = batch_size
         self._batch_flush_timeout = batch_timeout
 
+    @classmethod
+    def from_config(cls, config, nccl_coordinator=None, **kwargs) -> "V0KVTransferManager":
+        """A manager using the transfer method and peer direction of a
+        V0KVCacheConfig (the reference passes `kv_transfer_method` as a string,
+        elasticmm/engine/v0/config.py:35)."""
+        config.validate()
+        return cls(transfer_method=config.transfer_method, nccl_coordinator=nccl_coordinator,
+                   peer_direction=config.peer_direction, **kwargs)
+
     # -- registry --------------------------------------------------------------
     @staticmethod
     def _normalize_stage(stage: Any) -> str:

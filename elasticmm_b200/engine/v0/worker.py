@@ -38,7 +38,8 @@ def _range(name: str):
 
 
 _DTYPES = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16,
-           "float32": torch.float32, "float": torch.float32}
+           "float32": torch.float32, "float": torch.float32,
+           "uint8": torch.uint8, "int8": torch.int8, "fp8": torch.uint8, "float8": torch.uint8}
 
 
 class V0Worker:
@@ -96,18 +97,47 @@ class V0Worker:
 
     # -- pool set-up -----------------------------------------------------------
     def init_kvcache(self, num_gpu_blocks: int, num_layers: int, num_kv_heads: int, head_size: int,
-                     num_cpu_blocks: int = 0) -> None:
-        """Allocates the pool in the reference layout: L tensors [2, NB, BS, H, D].
+                     num_cpu_blocks: int = 0, layout: str = "nhd") -> None:
+        """Allocates the pool: L tensors of logical shape [2, NB, BS, H, D].
 
-        In the reference the tensors come from vLLM's CacheEngine
+        layout "nhd" is the reference's token-major allocation; "hnd" allocates
+        [2, NB, H, BS, D] and binds its permuted view, so indexing stays the
+        same and each head's tokens are contiguous. In the reference the
+        tensors come from vLLM's CacheEngine
         (elasticmm/engine/v0/worker.py:369-394); use bind_kv_cache to adopt those.
         """
+        if layout not in ("nhd", "hnd"):
+            raise ValueError(f"unknown pool layout {layout!r}")
         dt = _DTYPES[self.dtype]
-        shape = (2, num_gpu_blocks, self.block_size, num_kv_heads, head_size)
-        self.bind_kv_cache([torch.empty(shape, dtype=dt, device=self.device) for _ in range(num_layers)])
+
+        def alloc(nb: int, pinned: bool) -> torch.Tensor:
+            if layout == "nhd":
+                shape = (2, nb, self.block_size, num_kv_heads, head_size)
+            else:
+                shape = (2, nb, num_kv_heads, self.block_size, head_size)
+            t = torch.empty(shape, dtype=dt).pin_memory() if pinned else torch.empty(shape, dtype=dt,
+                                                                                     device=self.device)
+            return t if layout == "nhd" else t.permute(0, 1, 3, 2, 4)
+
+        self.bind_kv_cache([alloc(num_gpu_blocks, False) for _ in range(num_layers)])
         if num_cpu_blocks > 0:
-            cshape = (2, num_cpu_blocks, self.block_size, num_kv_heads, head_size)
-            self.bind_kv_swap([torch.empty(cshape, dtype=dt).pin_memory() for _ in range(num_layers)])
+            self.bind_kv_swap([alloc(num_cpu_blocks, True) for _ in range(num_layers)])
+
+    @classmethod
+    def from_config(cls, config, worker_id: int = 0, stage: EngineStage = EngineStage.PREFILL,
+                    device: Optional[torch.device] = None, global_rank: Optional[int] = None,
+                    world_size: Optional[int] = None, num_gpu_blocks: Optional[int] = None,
+                    num_cpu_blocks: Optional[int] = None) -> "V0Worker":
+        """A worker with its pool allocated from a V0KVCacheConfig (block
+        counts default to the configuration's maxima)."""
+        config.validate()
+        w = cls(worker_id=worker_id, stage=stage, block_size=config.block_size, dtype=config.dtype,
+                device=device, global_rank=global_rank, world_size=world_size)
+        w.init_kvcache(config.max_num_gpu_blocks if num_gpu_blocks is None else num_gpu_blocks,
+                       config.num_layers, config.num_kv_heads, config.head_size,
+                       num_cpu_blocks=config.max_num_cpu_blocks if num_cpu_blocks is None else num_cpu_blocks,
+                       layout=config.layout)
+        return w
 
     def bind_kv_cache(self, kv_cache: Sequence[torch.Tensor]) -> None:
         """Adopts an existing list of per-layer pool tensors (not copied)."""

@@ -159,3 +159,44 @@ def test_manager_batching_on_gpu(method):
     assert mgr.flush()                                                                          # the last two
     assert src.ctx.launch_count - launches == (4 if method == TransferMethod.P2P_COPY else 2)
     assert pools_equal(dst.kv_cache, dst_cpu)
+
+
+@pytest.mark.parametrize("layout", ["nhd", "hnd"])
+def test_worker_and_manager_from_config(layout):
+    from elasticmm_b200.engine.v0 import V0KVCacheConfig
+    cfg = V0KVCacheConfig(block_size=16, max_num_gpu_blocks=48, max_num_cpu_blocks=8, dtype="bfloat16",
+                          kv_transfer_method="b200_peer", num_layers=3, num_kv_heads=4, head_size=64,
+                          layout=layout)
+    src = V0Worker.from_config(cfg, worker_id=0, stage=EngineStage.PREFILL, device="cuda:0", global_rank=0)
+    dst = V0Worker.from_config(cfg, worker_id=1, stage=EngineStage.DECODING, device="cuda:0", global_rank=1)
+    assert len(src.kv_cache) == 3 and tuple(src.kv_cache[0].shape) == (2, 48, 16, 4, 64)
+    assert src.kv_cache[0].is_contiguous() == (layout == "nhd")
+    assert len(src.kv_swap) == 3 and tuple(src.kv_swap[0].shape) == (2, 8, 16, 4, 64)
+    assert sum(t.numel() * t.element_size() for t in src.kv_cache) == cfg.pool_bytes()
+    src_cpu = kv_oracle.make_pool(3, 48, 16, 4, 64, torch.bfloat16, 21)
+    dst_cpu = kv_oracle.make_pool(3, 48, 16, 4, 64, torch.bfloat16, 0, fill="guard")
+    for w, cpu in ((src, src_cpu), (dst, dst_cpu)):
+        for t, c in zip(w.kv_cache, cpu):
+            t.copy_(c)
+    # append through the slot mapping, then move the request with the configured method
+    g = torch.Generator().manual_seed(5)
+    key = torch.randn(20, 4, 64, generator=g).to(torch.bfloat16)
+    value = torch.randn(20, 4, 64, generator=g).to(torch.bfloat16)
+    table = [7, 40]
+    slots = torch.tensor(kv_oracle.slot_mapping_from_table(table, range(20), 16))
+    for layer in range(3):
+        src.reshape_and_cache(key.cuda(), value.cuda(), slots.cuda(), layer)
+        kv_oracle.reshape_and_cache(key, value, src_cpu[layer], slots)
+    mgr = V0KVTransferManager.from_config(cfg)
+    assert mgr.transfer_method == TransferMethod.B200_PEER and mgr.peer_direction == "pull"
+    mgr.register_worker(0, src, "prefill")
+    mgr.register_worker(1, dst, "decoding")
+    assert mgr.transfer_kv_cache_sync("r", 0, 1, table, [3, 4])
+    kv_oracle.copy_blocks(src_cpu, dst_cpu, table, [3, 4])
+    # and a swap out of the sink's new blocks into its pinned pool
+    dst.swap_blocks(["r"], [3, 4], [0, 5], False)
+    dst.wait_for_all_swap_out()
+    assert_clean(src.ctx)
+    assert pools_equal(src.kv_cache, src_cpu) and pools_equal(dst.kv_cache, dst_cpu)
+    for layer in range(3):
+        assert kv_oracle.bit_equal(dst.kv_swap[layer][:, [0, 5]], dst_cpu[layer][:, [3, 4]])

@@ -291,3 +291,33 @@ def test_manager_batching_merges_a_pair_into_one_transfer():
         torch.cuda.synchronize = real_sync
     assert seen == [5, 1]                       # one metrics sample per merged transfer
     assert mgr.get_stats()["transfer_count"] == 1   # the first (cold) merged transfer is not averaged
+
+
+def test_kv_cache_config_mirrors_the_reference_fields():
+    from elasticmm_b200.engine.v0 import DEFAULT_V0_KV_CONFIG, V0KVCacheConfig
+    d = DEFAULT_V0_KV_CONFIG
+    d.validate()
+    # defaults of the shared fields are the reference's (elasticmm/engine/v0/config.py:25-35)
+    assert (d.block_size, d.max_num_gpu_blocks, d.max_num_cpu_blocks, d.dtype, d.kv_transfer_method) == \
+        (16, 5000, 1000, "float16", "p2p_copy")
+    assert d.transfer_method is TransferMethod.P2P_COPY
+    # a dictionary written for the reference's V0EngineConfig loads; its other fields are ignored
+    ref_style = {"model_path": "m", "num_prefill_workers": 4, "block_size": 32, "max_num_gpu_blocks": 100,
+                 "max_num_cpu_blocks": 0, "dtype": "bfloat16", "tensor_parallel_size": 1,
+                 "gpu_memory_utilization": 0.9, "kv_transfer_method": "nccl"}
+    c = V0KVCacheConfig.from_dict(ref_style)
+    c.validate()
+    assert c.block_size == 32 and c.transfer_method is TransferMethod.NCCL
+    assert V0KVCacheConfig.from_dict(c.to_dict()) == c
+    with pytest.raises(TypeError, match="unexpected configuration keys"):
+        V0KVCacheConfig.from_dict({"blok_size": 16})
+    for bad in (dict(kv_transfer_method="rdma"), dict(block_size=0), dict(layout="dhn"), dict(dtype="int4"),
+                dict(peer_direction="both")):
+        with pytest.raises(AssertionError):
+            V0KVCacheConfig(**bad).validate()
+    V0KVCacheConfig(kv_transfer_method="b200_peer", peer_direction="push").validate()
+    # sizes: Llama-7B shape, 16-token blocks, fp16 -> 128 KiB pages, 8 MiB per block id
+    assert d.page_bytes == 128 * 1024 and d.block_bytes == 8 << 20
+    assert d.pool_bytes(8192) == 64 << 30
+    assert d.blocks_for_bytes(10 << 30) == 1280 and d.blocks_for_bytes(1 << 50) == 5000
+    assert d.blocks_for_tokens(2048) == 128 and d.blocks_for_tokens(2049) == 129
