@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
     "-cudart", "static",
-    "-ldl",
+    "-ldl", "-lpthread",
 ]
 
 

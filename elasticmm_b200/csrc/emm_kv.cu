@@ -7,9 +7,11 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -98,7 +100,6 @@ struct emm_ctx {
   int max_ctas = 0;
   int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
   int l2_hint = 0;                    // bulk family: bit 0 loads, bit 1 stores carry an L2 evict-first hint
-  int bulk_smem_set = 0;    // dynamic smem limit already applied to the bulk kernel
   IdSlot ring[kRingSlots];
   int next_slot = 0;
   std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
@@ -198,6 +199,16 @@ bool bitmap_mark(std::vector<uint64_t> &bm, const int64_t *ids, int32_t n, int64
   }
   return true;
 }
+int bitmap_reserve(std::vector<uint64_t> &bm, int64_t num_blocks) {
+  const size_t words = ((size_t)num_blocks + 63) / 64;
+  if (bm.size() >= words) return EMM_OK;
+  try {
+    bm.resize(words);
+  } catch (const std::bad_alloc &) {
+    return fail(EMM_ERR_NOMEM, "no host memory for a bitmap of %lld blocks", (long long)num_blocks);
+  }
+  return EMM_OK;
+}
 void bitmap_clear(std::vector<uint64_t> &bm, const int64_t *ids, int32_t n) {
   for (int32_t i = 0; i < n; ++i) bm[(uint64_t)ids[i] >> 6] = 0;
 }
@@ -240,6 +251,32 @@ CopySide packed_side(const void *packed, int32_t n, int64_t page, int planes = 2
   s.num_segs = 0;
   s.seg_stride = 0;
   return s;
+}
+
+// The dynamic shared-memory limit of a kernel belongs to (kernel, device) and is
+// shared by every context and entry point of the process, so it is tracked per
+// device and only ever raised: lowering it under a caller that already sized
+// its launches for the larger value would make those launches fail.
+constexpr int kMaxTrackedDevices = 64;
+std::atomic<int> g_bulk_smem_limit[kMaxTrackedDevices];
+std::mutex g_bulk_smem_mutex;
+
+// Call with `device` current.
+int ensure_bulk_smem(int device, int smem) {
+  const bool tracked = device >= 0 && device < kMaxTrackedDevices;
+  if (tracked && smem <= g_bulk_smem_limit[device].load(std::memory_order_acquire)) return EMM_OK;
+  std::lock_guard<std::mutex> lock(g_bulk_smem_mutex);
+  int current = tracked ? g_bulk_smem_limit[device].load(std::memory_order_relaxed) : 0;
+  if (!tracked) {
+    cudaFuncAttributes fa;
+    EMM_CUDA(cudaFuncGetAttributes(&fa, emm::page_copy_bulk<false>));
+    current = fa.maxDynamicSharedSizeBytes;
+  }
+  if (smem <= current) return EMM_OK;
+  EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  if (tracked) g_bulk_smem_limit[device].store(smem, std::memory_order_release);
+  return EMM_OK;
 }
 
 template <typename V, bool kSeg>
@@ -319,13 +356,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
 
   if (variant == EMM_COPY_BULK) {
     const int smem = (int)((int64_t)warps * ctx->stages * chunk);
-    if (smem > ctx->bulk_smem_set) {
-      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      ctx->bulk_smem_set = smem;
-    }
+    if (int rc = ensure_bulk_smem(ctx->device, smem)) return rc;
     const int fit = std::max(1, (int)((ctx->max_smem_optin - 2048) / (smem + 1024)));
     int per_sm = ctx->ctas_per_sm > 0 ? ctx->ctas_per_sm : (auto_ctas_per_sm > 0 ? auto_ctas_per_sm : fit);
     per_sm = std::min(std::min(per_sm, fit), 2048 / (warps * 32));
@@ -791,8 +822,7 @@ int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d
   if (int rc = check_ids_host(h_ids, n, pool->desc.num_blocks, "scatter")) return rc;
   if (n == 0) return packed_copy(pool, false, 0, pool->desc.num_layers, nullptr, 0, d_packed, packed_bytes, stream);
   emm_ctx *ctx = pool->ctx;
-  const size_t words = ((size_t)pool->desc.num_blocks + 63) / 64;
-  if (ctx->bitmap.size() < words) ctx->bitmap.resize(words);
+  if (int rc = bitmap_reserve(ctx->bitmap, pool->desc.num_blocks)) return rc;
   int64_t dup = -1;
   const bool unique = bitmap_mark(ctx->bitmap, h_ids, n, &dup);
   bitmap_clear(ctx->bitmap, h_ids, n);
@@ -816,8 +846,7 @@ int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
   if (int rc = check_ids_host(h_src_ids, n, src->desc.num_blocks, "copy_blocks source")) return rc;
   if (int rc = check_ids_host(h_dst_ids, n, dst->desc.num_blocks, "copy_blocks destination")) return rc;
   emm_ctx *ctx = src->ctx;
-  const size_t words = ((size_t)std::max(src->desc.num_blocks, dst->desc.num_blocks) + 63) / 64;
-  if (ctx->bitmap.size() < words) ctx->bitmap.resize(words);
+  if (int rc = bitmap_reserve(ctx->bitmap, std::max(src->desc.num_blocks, dst->desc.num_blocks))) return rc;
   int64_t dup = -1;
   bool ok = bitmap_mark(ctx->bitmap, h_dst_ids, n, &dup);
   int rc_check = EMM_OK;
@@ -941,8 +970,13 @@ int emm_compact_plan(const int64_t *table_ids, int64_t n_ids, int64_t num_blocks
   if (n_ids > num_blocks)
     return fail(EMM_ERR_LENGTH, "compact_plan: %lld live ids in a pool of %lld blocks", (long long)n_ids,
                 (long long)num_blocks);
-  // occupied[b] for b < n_ids: a live block already sits in the dense prefix.
-  std::vector<uint8_t> seen((size_t)num_blocks, 0);
+  // seen[b]: block b is live; for b < n_ids it already sits in the dense prefix.
+  std::vector<uint8_t> seen;
+  try {
+    seen.assign((size_t)num_blocks, 0);
+  } catch (const std::bad_alloc &) {
+    return fail(EMM_ERR_NOMEM, "compact_plan: no host memory for %lld flags", (long long)num_blocks);
+  }
   for (int64_t i = 0; i < n_ids; ++i) {
     const int64_t id = table_ids[i];
     if (id < 0 || id >= num_blocks)
@@ -1056,7 +1090,7 @@ typedef const char *(*nccl_error_string_fn)(int);
 constexpr int kNcclInt8 = 0;  // ncclInt8 / ncclChar
 
 struct NcclApi {
-  bool tried = false;
+  std::once_flag once;
   void *lib = nullptr;
   nccl_get_unique_id_fn get_unique_id = nullptr;
   nccl_comm_init_rank_fn comm_init_rank = nullptr;
@@ -1071,8 +1105,7 @@ NcclApi g_nccl;
 
 int nccl_api(NcclApi **out) {
   NcclApi &a = g_nccl;
-  if (!a.tried) {
-    a.tried = true;
+  std::call_once(a.once, [&a] {
     const char *override_path = getenv("EMM_NCCL_LIB");
     // Prefer the copy the process has already loaded (the host framework's), then the search path.
     if (override_path && *override_path) a.lib = dlopen(override_path, RTLD_NOW | RTLD_GLOBAL);
@@ -1088,7 +1121,7 @@ int nccl_api(NcclApi **out) {
       a.group_end = (nccl_group_fn)dlsym(a.lib, "ncclGroupEnd");
       a.error_string = (nccl_error_string_fn)dlsym(a.lib, "ncclGetErrorString");
     }
-  }
+  });
   if (!a.lib || !a.get_unique_id || !a.comm_init_rank || !a.comm_destroy || !a.send || !a.recv ||
       !a.group_start || !a.group_end)
     return fail(EMM_ERR_NCCL, "libnccl.so.2 could not be loaded (set EMM_NCCL_LIB to its path): %s",
@@ -1296,7 +1329,6 @@ struct NoAllocDevice {
   unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on this device
   int sm_count = 0;
   int max_smem_optin = 0;
-  int smem_set = 0;
 };
 NoAllocDevice g_noalloc_dev[kNaMaxDevices];
 
@@ -1407,10 +1439,7 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
     const int smem = (int)(warps * stages * chunk);
     if (smem > nd->max_smem_optin - 2048)
       return fail(EMM_ERR_BAD_ARG, "gather_noalloc: ring does not fit shared memory");
-    if (smem > nd->smem_set) {
-      EMM_CUDA(cudaFuncSetAttribute(emm::page_copy_bulk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      nd->smem_set = smem;
-    }
+    if (int rc = ensure_bulk_smem(device, smem)) return rc;
     const uint64_t want_ctas = (a.total_chunks + warps - 1) / warps;
     const int grid = (int)std::min<uint64_t>(want_ctas, (uint64_t)nd->sm_count * per_sm);
     emm::page_copy_bulk<false><<<grid, warps * 32, smem, st>>>(a, (uint32_t)stages, 0u);

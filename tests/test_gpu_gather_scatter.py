@@ -240,3 +240,22 @@ def test_many_requests_in_one_launch(ctx, opts, case):
         src.extract_kv_blocks_many([[0], [case["NB"]]])
     with pytest.raises(EmmError):
         dst.write_kv_blocks_many([[1], [1]], src.extract_kv_blocks_many([[0], [1]]))
+
+
+def test_two_contexts_on_one_device_share_the_kernel_shared_memory_limit():
+    """The dynamic shared-memory limit belongs to the kernel and the device, not
+    to a context: a second context with a small ring must not lower it under
+    the first one's 128 KiB launches."""
+    from elasticmm_b200.kv_pool import Context
+    first = get_context(0)
+    configure(first, **BULK_DEFAULT)
+    second = Context(0)
+    second.configure(variant=_lib.COPY_BULK, chunk_bytes=4096, stages=2, warps=1)
+    cpu = kv_oracle.make_pool(2, 24, 16, 32, 128, torch.float16, 9)      # 128 KiB pages
+    gpu = to_gpu(cpu)
+    ids = [5, 0, 23, 11, 12]
+    want = kv_oracle.extract_kv_blocks(cpu, ids)
+    for ctx in (first, second, first, second):
+        got = KVPool(gpu, ctx).gather(ids)
+        assert_clean(ctx)
+        assert kv_oracle.bit_equal(got.cpu(), want)

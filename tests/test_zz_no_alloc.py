@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from elasticmm_b200 import KVPool, _lib, get_context
+from gpu_util import BULK_DEFAULT, configure
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu
@@ -47,6 +48,24 @@ def test_two_calls_in_a_row_match_the_allocating_entry(geom):
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))    # bit-exact, as every parity test here
         assert kv_oracle.bit_equal(got.cpu(), kv_oracle.extract_kv_blocks(cpu, ids))
+    assert ctx.status()[0] == _lib.OK
+
+
+def test_a_small_ring_here_leaves_the_larger_launches_of_a_context_working():
+    """Both entry points launch the same kernel, whose shared-memory limit is
+    per device: a 16 KiB-page call here (96 KiB ring) between two 128 KiB-ring
+    gathers of a context must not make the second one fail."""
+    ctx = get_context(0)
+    configure(ctx, **BULK_DEFAULT)
+    big_cpu = kv_oracle.make_pool(2, 16, 16, 32, 128, torch.float16, 4)      # 128 KiB pages
+    small_cpu = kv_oracle.make_pool(2, 16, 16, 4, 128, torch.float16, 5)     # 16 KiB pages
+    big, small = KVPool([t.cuda() for t in big_cpu], ctx), KVPool([t.cuda() for t in small_cpu], ctx)
+    ids = [3, 9, 1]
+    assert kv_oracle.bit_equal(big.gather(ids).cpu(), kv_oracle.extract_kv_blocks(big_cpu, ids))
+    got = small.new_packed(len(ids))
+    assert _noalloc_gather(small, ids, got) == _lib.OK, _lib.last_error()
+    assert kv_oracle.bit_equal(got.cpu(), kv_oracle.extract_kv_blocks(small_cpu, ids))
+    assert kv_oracle.bit_equal(big.gather(ids).cpu(), kv_oracle.extract_kv_blocks(big_cpu, ids))
     assert ctx.status()[0] == _lib.OK
 
 
