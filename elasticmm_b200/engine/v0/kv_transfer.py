@@ -49,7 +49,7 @@ class V0KVTransferManager:
         self.peer_direction = peer_direction  # B200_PEER: the sink loads (default) or the source stores
         self.transfer_method = transfer_method
         self.nccl_coordinator = nccl_coordinator
-        self.enable_batching = enable_batching  # kept for signature parity; see transfer_many
+        self.enable_batching = enable_batching  # queue transfers per (source, sink) pair; see flush()
         self.metrics_callback = metrics_callback
         self.worker_registry: Dict[int, Any] = {}
         self.rank_to_stage: Dict[int, str] = {}
@@ -58,6 +58,7 @@ class V0KVTransferManager:
         self.total_transfer_time = 0.0
         self.total_bytes_transferred = 0
         self.first_transfer_done = False
+        self.last_result: Dict[str, Any] = {}  # what the most recent transfer returned (bytes, blocks or error)
         self._host_stage: Optional[torch.Tensor] = None  # pinned buffer of the staged_copy method
         # batching: small transfers of one (source, sink) pair are merged into one table
         self._transfer_queue: Dict[tuple, List[tuple]] = {}
