@@ -204,6 +204,17 @@ def timed(fn, steps, warmup, device, barrier=None):
 # CPU baseline (oracle port of the reference's torch index/copy path)
 # ---------------------------------------------------------------------------
 
+def cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 class CpuPath:
     """gather -> scatter of a workload's geometry on host tensors with the oracle port of the
     reference's torch index/copy path, all torch threads. Bounded: a reduced pool (about 3 GiB)
@@ -253,8 +264,7 @@ class CpuPath:
                 "sample": f"{reqs} requests ({moved} blocks, {moved * block_bytes(w) / GIB:.1f} GiB payload) of "
                           f"{self.wname} geometry on a {nb}-block host pool; extract_kv_blocks then write_kv_blocks "
                           f"restated with torch CPU indexing; {self.threads} torch threads, {os.cpu_count()} host cpus",
-                "seconds": round(t_total, 2), "blocks_per_s": round(moved / t_total, 1)}
-
+                "seconds": round(t_total, 2), "blocks_per_s": round(moved / t_total, 1), "cpu_model": cpu_model()}
 
     def run_c(self, budget_s):
         """The same requests with the plain-C restatement (one memcpy per page, all host threads)."""
