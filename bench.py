@@ -435,12 +435,26 @@ def bench_single(args):
             dst.scatter_many_from(d_tab, many_flat)
 
     ms_many = timed(step_many, direct_steps, 3, device)
+    del many_flat
+    # the same through the worker methods with host id lists (tables built, staged and uploaded inside the timed region)
+    wave_lists, pos = [], 0
+    for wave in waves:
+        wave_lists.append(([reqs[pos + k][0] for k in range(len(wave))], [reqs[pos + k][1] for k in range(len(wave))]))
+        pos += len(wave)
+
+    def step_many_api():
+        for s_lists, d_lists in wave_lists:
+            dst_worker.write_kv_blocks_many(d_lists, src_worker.extract_kv_blocks_many(s_lists))
+        rc, _ = ctx.status()
+        assert rc == 0
+
+    ms_many_api = timed(step_many_api, direct_steps, 3, device)
     ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3, device)
     e2e_steps = max(3, args.steps // 4)
     e2e_value = payload * e2e_steps / (ms_e2e / 1e3) / 1e9
     h2d = sum(4 * (len(s) + len(d)) for s, d in reqs)
 
-    del packed, flat, dev_tables, wave_tables, many, many_flat
+    del packed, flat, dev_tables, wave_tables, many
     extras = {}
     if not args.skip_extras:
         src_worker = dst_worker = src = dst = None
@@ -491,7 +505,12 @@ def bench_single(args):
                 "hbm_gbs": round(4 * payload * direct_steps / (ms_many / 1e3) / 1e9, 1),
                 "ms_per_step": round(ms_many / direct_steps, 3), "launches_per_step": 2 * len(waves),
                 "path": "gather into one contiguous buffer per request, then scatter, all requests of a wave in one "
-                        "launch per direction (emm_gather_many / emm_scatter_many)"}},
+                        "launch per direction (emm_gather_many / emm_scatter_many)",
+                "through_worker_api": {
+                    "value": round(payload * direct_steps / (ms_many_api / 1e3) / 1e9, 2), "unit": "GB/s",
+                    "ms_per_step": round(ms_many_api / direct_steps, 3),
+                    "api": "V0Worker.extract_kv_blocks_many + write_kv_blocks_many per wave, host id lists, "
+                           "output tensors allocated per call"}}},
     }
     line.update(extras)
     print(json.dumps(line))
