@@ -15,7 +15,7 @@ import importlib
 import os
 import sys
 import types
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import torch
 

@@ -1,7 +1,5 @@
 """Helpers shared by the GPU parity tests."""
-import torch
-
-from elasticmm_b200 import KVPool, _lib, get_context
+from elasticmm_b200 import _lib
 from oracle import kv_oracle
 
 VARIANTS = [

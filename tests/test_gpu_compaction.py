@@ -2,9 +2,9 @@
 import pytest
 import torch
 
-from elasticmm_b200 import KVPool, get_context
+from elasticmm_b200 import get_context
 from elasticmm_b200.engine.v0 import Request, V0BlockManager, V0Worker
-from gpu_util import BULK_DEFAULT, LDG_DEFAULT, VARIANTS, assert_clean, configure, pools_equal, to_gpu, vid
+from gpu_util import BULK_DEFAULT, LDG_DEFAULT, assert_clean, configure, pools_equal, to_gpu, vid
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from elasticmm_b200 import KVPool, get_context
-from gpu_util import BULK_DEFAULT, LDG_DEFAULT, assert_clean, configure, pools_equal, to_gpu, vid
+from gpu_util import BULK_DEFAULT, LDG_DEFAULT, assert_clean, configure, pools_equal, vid
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu

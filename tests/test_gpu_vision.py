@@ -4,9 +4,9 @@ import asyncio
 import pytest
 import torch
 
-from elasticmm_b200 import EmmError, KVPool, _lib, get_context
+from elasticmm_b200 import EmmError, KVPool, get_context
 from elasticmm_b200.engine.v0 import NCCLCoordinator, TransferMethod, V0KVTransferManager, V0Worker
-from gpu_util import BULK_DEFAULT, LDG_DEFAULT, VARIANTS, assert_clean, configure, vid
+from gpu_util import BULK_DEFAULT, LDG_DEFAULT, assert_clean, configure, vid
 from oracle import kv_oracle
 
 pytestmark = pytest.mark.gpu

@@ -4,9 +4,8 @@ import asyncio
 import pytest
 import torch
 
-from elasticmm_b200 import _lib, get_context
-from elasticmm_b200.engine.v0 import (EngineStage, KVTransferMetrics, MigrationPlan, Request, Transfer,
-                                      TransferMethod, V0BlockManager, V0KVTransferManager, V0Worker)
+from elasticmm_b200 import get_context
+from elasticmm_b200.engine.v0 import (EngineStage, KVTransferMetrics, Request, TransferMethod, V0BlockManager, V0KVTransferManager, V0Worker)
 from gpu_util import assert_clean, configure, pools_equal, to_gpu
 from oracle import kv_oracle
 

@@ -11,7 +11,6 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-import cases
 from elasticmm_b200.engine.v0.transport import (MigrationPlan, Transfer, plan_chunks, pipelined_recv,
                                                 pipelined_send)
 from oracle import kv_oracle
