@@ -81,3 +81,46 @@ def test_nccl_entries_validate_arguments_without_a_gpu():
     assert lib.emm_exchange(None, 1, None, None, None, None, None) == _lib.ERR_BAD_ARG
     assert lib.emm_nccl_comm_destroy(None) == _lib.OK
     assert lib.emm_send_blocks(None, None, 0, None, 0, None, 0, 1, None) == _lib.ERR_BAD_ARG
+
+
+C_CLIENT = r"""
+#include <stdio.h>
+#include "emm_kv.h"
+
+int main(void) {
+  emm_pool_desc d;
+  int64_t table[5] = {9, 1, 7, 0, 4}, new_ids[5], src[5], dst[5], moves = -1;
+  if (emm_abi_version() != EMM_KV_ABI_VERSION) return 1;
+  if (emm_pool_desc_hnd(&d, 28, 64, 16, 4, 128, 2) != EMM_OK) return 2;
+  if (d.token_stride != 256 || d.head_stride != 16 * 256 || d.num_planes != 2) return 3;
+  if (emm_pool_desc_nhd(&d, 1, 1, 1, 1, 1, 3) != EMM_ERR_BAD_ARG) return 4;
+  if (emm_compact_plan(table, 5, 10, new_ids, src, dst, &moves) != EMM_OK || moves != 2) return 5;
+  printf("%lld->%lld %lld->%lld %s\n", (long long)src[0], (long long)dst[0], (long long)src[1],
+         (long long)dst[1], emm_status_string(EMM_ERR_TIMEOUT));
+  return 0;
+}
+"""
+
+
+def test_header_is_plain_c_and_a_c_program_links_against_the_library(tmp_path):
+    """An integrator may bind the ABI from C: the header must compile as C99 and
+    as C++ without warnings, and a C client must link and run (host-only entries)."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    inc = os.path.dirname(HEADER)
+    _lib.load()
+    libdir = str(_lib.LIB_PATH.parent)
+    src = tmp_path / "client.c"
+    src.write_text(C_CLIENT)
+    flags = ["-Wall", "-Wextra", "-pedantic", "-Werror", "-I", inc]
+    subprocess.run(["gcc", "-std=c99", *flags, "-fsyntax-only", str(src)], check=True)
+    if shutil.which("g++"):
+        subprocess.run(["g++", "-std=c++11", *flags, "-fsyntax-only", "-x", "c++", str(src)], check=True)
+    exe = tmp_path / "client"
+    subprocess.run(["gcc", "-std=c99", *flags, str(src), "-o", str(exe), "-L", libdir, "-lemm_kv",
+                    f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    assert out.strip() == "9->2 7->3 device-side wait timed out"
