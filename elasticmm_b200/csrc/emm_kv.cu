@@ -115,6 +115,7 @@ struct emm_ctx {
 
 struct emm_pool {
   emm_ctx *ctx = nullptr;
+  int device = 0;  // copy of ctx->device: destroying a pool must not need a live context
   emm_pool_desc desc{};
   uint64_t *d_layers = nullptr;
   std::vector<uint64_t> h_layers;
@@ -675,6 +676,7 @@ int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *
   emm_pool *p = new (std::nothrow) emm_pool();
   if (!p) return fail(EMM_ERR_NOMEM, "emm_pool_create: host allocation failed");
   p->ctx = ctx;
+  p->device = ctx->device;
   p->desc = *desc;
   p->planes = desc->num_planes == 1 ? 1 : 2;
   p->desc.num_planes = p->planes;
@@ -719,7 +721,7 @@ int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *
 
 int emm_pool_destroy(emm_pool *pool) {
   if (!pool) return EMM_OK;
-  DeviceGuard guard(pool->ctx->device);
+  DeviceGuard guard(pool->device);
   if (pool->d_layers) cudaFree(pool->d_layers);
   delete pool;
   return EMM_OK;

@@ -141,6 +141,8 @@ int emm_pool_desc_blocks(emm_pool_desc *desc, int L, int NB, int rows, int cols,
  * (elasticmm/engine/v0/worker.py:635-647). */
 int emm_pool_create(emm_ctx *ctx, const emm_pool_desc *desc, const void *const *layer_ptrs,
                     emm_pool **out);
+/* Frees the library's part of a pool (its device copy of the layer pointers). A pool may be
+ * destroyed after its context, but must not be used for a launch after it. */
 int emm_pool_destroy(emm_pool *pool);
 int emm_pool_get_desc(const emm_pool *pool, emm_pool_desc *desc);
 /* Bytes of one block of one plane of one layer (BS*H*D*elem_size). */

@@ -259,3 +259,15 @@ def test_two_contexts_on_one_device_share_the_kernel_shared_memory_limit():
         got = KVPool(gpu, ctx).gather(ids)
         assert_clean(ctx)
         assert kv_oracle.bit_equal(got.cpu(), want)
+
+
+def test_a_pool_may_be_destroyed_after_its_context():
+    from elasticmm_b200.kv_pool import Context
+    ctx = Context(0)
+    cpu = kv_oracle.make_pool(2, 8, 4, 2, 8, torch.float16, 3)
+    pool = KVPool(to_gpu(cpu), ctx)
+    assert kv_oracle.bit_equal(pool.gather([1, 6]).cpu(), kv_oracle.extract_kv_blocks(cpu, [1, 6]))
+    torch.cuda.synchronize()
+    ctx.close()
+    pool.close()      # frees the pool's device array without touching the closed context
+    pool.close()      # and closing twice is harmless
