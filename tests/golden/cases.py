@@ -48,6 +48,42 @@ KV_CASES = [
 ]
 
 
+# Per-token append (reshape_and_cache). The expected pools come from vLLM's own cache op
+# (vllm._custom_ops.reshape_and_cache_flash, the op behind the reference's
+# model_runner.execute_model, elasticmm/engine/v0/worker_steps.py:281,438) run by
+# make_append_golden.py on a CUDA machine. pad_every > 0 sets every pad_every-th slot to -1.
+def _append_case(name, L, NB, BS, H, D, dtype, seed, T, pad_every, store="full"):
+    return dict(name=name, L=L, NB=NB, BS=BS, H=H, D=D, dtype=dtype, seed=seed, T=T, pad_every=pad_every,
+                store=store)
+
+
+APPEND_CASES = [
+    _append_case("gqa8_row_2KiB", 3, 12, 16, 8, 128, "bfloat16", 41, 37, 7, store="sha"),
+    _append_case("mha32_row_8KiB", 2, 6, 16, 32, 128, "float16", 42, 9, 4, store="sha"),
+    _append_case("odd_row_30B", 2, 33, 4, 3, 5, "float16", 43, 21, 5),
+    _append_case("fp32_row_48B", 2, 16, 8, 2, 6, "float32", 44, 5, 0),
+    _append_case("every_slot", 1, 5, 16, 1, 64, "bfloat16", 45, 80, 0),
+    _append_case("all_padding", 1, 4, 16, 2, 64, "float16", 46, 6, 1),
+    # BASELINE config 2's shape (256 tokens, 8 KV heads, head_dim 128, bf16, 32 layers, 1 % padding) on a
+    # pool cut to 128 blocks per layer; only the digest of the resulting pool is stored.
+    _append_case("cfg2_decode_batch_256", 32, 128, 16, 8, 128, "bfloat16", 47, 256, 100, store="sha"),
+]
+
+
+def build_append_inputs(case):
+    """(pool, key [L,T,H,D], value [L,T,H,D], slot_mapping [T] int64), all CPU tensors rebuilt from the seed."""
+    dt = _DT[case["dtype"]]
+    L, NB, BS, H, D, T = (case[k] for k in ("L", "NB", "BS", "H", "D", "T"))
+    pool = kv_oracle.make_pool(L, NB, BS, H, D, dt, case["seed"])
+    g = torch.Generator().manual_seed(case["seed"] + 1000)
+    key = torch.randn(L, T, H, D, generator=g).to(dt)
+    value = torch.randn(L, T, H, D, generator=g).to(dt)
+    slots = torch.randperm(NB * BS, generator=g)[:T].clone()
+    if case["pad_every"]:
+        slots[::case["pad_every"]] = -1
+    return pool, key, value, slots
+
+
 def build_pools(case):
     """(source pool, guard-filled destination pool) as lists of CPU tensors."""
     dt = _DT[case["dtype"]]

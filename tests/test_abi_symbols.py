@@ -44,6 +44,7 @@ def test_status_codes_match_header():
 
 def test_pool_desc_presets_need_no_gpu():
     lib = _lib.load()
+    assert C.sizeof(_lib.PoolDesc) == 64  # struct emm_pool_desc; the C client below checks the C side
     d = _lib.PoolDesc()
     assert lib.emm_pool_desc_nhd(C.byref(d), 32, 2048, 16, 32, 128, 2) == 0
     page = 16 * 32 * 128 * 2
@@ -91,6 +92,7 @@ int main(void) {
   emm_pool_desc d;
   int64_t table[5] = {9, 1, 7, 0, 4}, new_ids[5], src[5], dst[5], moves = -1;
   if (emm_abi_version() != EMM_KV_ABI_VERSION) return 1;
+  if (sizeof(emm_pool_desc) != 64) return 6;
   if (emm_pool_desc_hnd(&d, 28, 64, 16, 4, 128, 2) != EMM_OK) return 2;
   if (d.token_stride != 256 || d.head_stride != 16 * 256 || d.num_planes != 2) return 3;
   if (emm_pool_desc_nhd(&d, 1, 1, 1, 1, 1, 3) != EMM_ERR_BAD_ARG) return 4;
