@@ -44,6 +44,7 @@ OPT_LDG_UNROLL = 5
 OPT_MAX_CTAS = 6
 OPT_REMOTE_VARIANT = 7
 OPT_L2_HINT = 8
+OPT_WAIT_LIMIT_NS = 9
 
 
 class PoolDesc(C.Structure):
@@ -103,6 +104,9 @@ SIGNATURES = {
     "emm_scatter_layers": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_gather_many": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
     "emm_scatter_many": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
+    "emm_gather_many_layers": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
+    "emm_scatter_many_layers": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P, C.c_uint64, _P]),
+    "emm_test_gather_expect_overcount": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, C.c_uint32, _P]),
     "emm_copy_blocks": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P]),
     "emm_gather_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
     "emm_scatter_h": (C.c_int, [_P, _P, C.c_int32, _P, C.c_uint64, _P]),
@@ -113,6 +117,10 @@ SIGNATURES = {
         C.c_int,
         [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, _P, C.c_int32, _P],
     ),
+    "emm_append_bind": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, _P, C.c_int32, C.POINTER(_P)]),
+    "emm_append_bound": (C.c_int, [_P, C.c_int32, _P]),
+    "emm_append_unbind": (C.c_int, [_P]),
+    "emm_upload_ids": (C.c_int, [_P, _P, C.c_int32, _P, _P]),
     "emm_compact_plan": (C.c_int, [_I64P, C.c_int64, C.c_int64, _I64P, _I64P, _I64P, _I64P]),
     "emm_nccl_unique_id": (C.c_int, [C.c_char_p]),
     "emm_nccl_comm_init": (C.c_int, [_P, C.c_char_p, C.c_int, C.c_int, C.POINTER(_P)]),

@@ -100,6 +100,7 @@ struct emm_ctx {
   int max_ctas = 0;
   int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
   int l2_hint = 0;                    // bulk family: bit 0 loads, bit 1 stores carry an L2 evict-first hint
+  uint64_t wait_limit_ns = emm::kDefaultWaitLimitNs;  // bulk family: bound of each device-side wait
   IdSlot ring[kRingSlots];
   int next_slot = 0;
   std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
@@ -305,7 +306,7 @@ void launch_ldg(emm_ctx *ctx, const PageCopyArgs &a, int grid, uint32_t align, c
 // both sides are ordinary memory of this GPU.
 int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_t layer_begin,
                      int32_t layer_count, int64_t page_bytes, uint32_t align, bool local,
-                     cudaStream_t st, int planes = 2) {
+                     cudaStream_t st, int planes = 2, uint32_t tx_overcount = 0) {
   if (n == 0 || layer_count == 0) return EMM_OK;
   DeviceGuard guard(ctx->device);
   if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
@@ -313,6 +314,7 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   int variant = ctx->copy_variant;
   if (variant == EMM_COPY_AUTO) variant = EMM_COPY_BULK;
   if (!local) variant = ctx->remote_variant;
+  if (tx_overcount) variant = EMM_COPY_BULK;  // the test hook exists for the bulk family's wait only
   if (align < 16) variant = EMM_COPY_LDG;
 
   PageCopyArgs a;
@@ -324,6 +326,8 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   a.layer_count = (uint32_t)layer_count;
   a.page_bytes = (uint32_t)page_bytes;
   a.status = ctx->d_status;
+  a.wait_limit_ns = ctx->wait_limit_ns;
+  a.tx_overcount = tx_overcount;
   const bool segmented = src.seg_prefix != nullptr || dst.seg_prefix != nullptr;
 
   int64_t chunk = ctx->chunk_bytes;
@@ -402,7 +406,8 @@ int check_layer_range(const emm_pool *p, int32_t begin, int32_t count) {
 
 int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t layer_count,
                 const int32_t *d_ids, int32_t n, const void *d_packed, uint64_t packed_bytes,
-                void *stream, const uint32_t *d_seg_prefix = nullptr, int32_t num_segs = 0) {
+                void *stream, const uint32_t *d_seg_prefix = nullptr, int32_t num_segs = 0,
+                uint32_t tx_overcount = 0) {
   const char *what = to_packed ? "gather" : "scatter";
   if (int rc = check_pool_for_pages(pool, what)) return rc;
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
@@ -423,12 +428,13 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
     bs.num_segs = (uint32_t)num_segs;
     bs.seg_stride = (uint64_t)layer_count * (uint64_t)pool->planes * (uint64_t)pool->page_bytes;
   }
+  if (tx_overcount && align < 16) return fail(EMM_ERR_ALIGN, "%s: the wait test needs 16-byte granular pages", what);
   return to_packed ? launch_page_copy(pool->ctx, ps, bs, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream, pool->planes)
+                                      (cudaStream_t)stream, pool->planes, tx_overcount)
                    : launch_page_copy(pool->ctx, bs, ps, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream, pool->planes);
+                                      (cudaStream_t)stream, pool->planes, tx_overcount);
 }
 
 // Uploads host ids (already validated) into a ring slot; returns the device
@@ -568,6 +574,11 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       if (value < 0 || value > 3) return fail(EMM_ERR_BAD_ARG, "L2 hint must be in [0, 3]");
       ctx->l2_hint = (int)value;
       return EMM_OK;
+    case EMM_OPT_WAIT_LIMIT_NS:
+      if (value < 1000 || value > 60000000000ll)
+        return fail(EMM_ERR_BAD_ARG, "wait limit must be between 1 us and 60 s (in ns)");
+      ctx->wait_limit_ns = (uint64_t)value;
+      return EMM_OK;
     case EMM_OPT_REMOTE_VARIANT:
       if (value != EMM_COPY_BULK && value != EMM_COPY_LDG)
         return fail(EMM_ERR_BAD_ARG, "remote variant must be EMM_COPY_BULK or EMM_COPY_LDG");
@@ -590,6 +601,7 @@ int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
     case EMM_OPT_MAX_CTAS: *value = ctx->max_ctas; return EMM_OK;
     case EMM_OPT_REMOTE_VARIANT: *value = ctx->remote_variant; return EMM_OK;
     case EMM_OPT_L2_HINT: *value = ctx->l2_hint; return EMM_OK;
+    case EMM_OPT_WAIT_LIMIT_NS: *value = (int64_t)ctx->wait_limit_ns; return EMM_OK;
     default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
 }
@@ -761,25 +773,51 @@ int emm_scatter_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
   return packed_copy(pool, false, layer_begin, layer_count, d_ids, n, d_packed, packed_bytes, stream);
 }
 
-static int many_impl(emm_pool *pool, bool to_packed, const int32_t *d_ids, const uint32_t *d_seg_prefix,
-                     int32_t num_segs, int32_t n_total, const void *d_packed, uint64_t packed_bytes,
-                     void *stream) {
+int emm_test_gather_expect_overcount(emm_pool *pool, const int32_t *d_ids, int32_t n, void *d_packed,
+                                     uint64_t packed_bytes, uint32_t extra_tx_bytes, void *stream) {
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "gather: null pool");
+  if (extra_tx_bytes == 0 || extra_tx_bytes > (1u << 20))
+    return fail(EMM_ERR_BAD_ARG, "extra_tx_bytes must be in [1, 1 MiB]");
+  return packed_copy(pool, true, 0, pool->desc.num_layers, d_ids, n, d_packed, packed_bytes, stream, nullptr, 0,
+                     extra_tx_bytes);
+}
+
+static int many_impl(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t layer_count,
+                     const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs, int32_t n_total,
+                     const void *d_packed, uint64_t packed_bytes, void *stream) {
   if (!pool) return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: null pool");
   if (num_segs < 0 || n_total < 0) return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: negative count");
   if (n_total > 0 && (num_segs == 0 || !d_seg_prefix))
     return fail(EMM_ERR_BAD_ARG, "gather/scatter_many: blocks without segments");
-  return packed_copy(pool, to_packed, 0, pool->desc.num_layers, d_ids, n_total, d_packed, packed_bytes, stream,
+  if (layer_count < 0) layer_count = pool->desc.num_layers - layer_begin;
+  return packed_copy(pool, to_packed, layer_begin, layer_count, d_ids, n_total, d_packed, packed_bytes, stream,
                      d_seg_prefix, num_segs);
 }
 
 int emm_gather_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
                     int32_t n_total, void *d_packed, uint64_t packed_bytes, void *stream) {
-  return many_impl(pool, true, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
+  return many_impl(pool, true, 0, -1, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
 }
 
 int emm_scatter_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
                      int32_t n_total, const void *d_packed, uint64_t packed_bytes, void *stream) {
-  return many_impl(pool, false, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
+  return many_impl(pool, false, 0, -1, d_ids, d_seg_prefix, num_segs, n_total, d_packed, packed_bytes, stream);
+}
+
+int emm_gather_many_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const int32_t *d_ids,
+                           const uint32_t *d_seg_prefix, int32_t num_segs, int32_t n_total, void *d_packed,
+                           uint64_t packed_bytes, void *stream) {
+  if (layer_count < 0) return fail(EMM_ERR_BAD_ARG, "gather_many_layers: negative layer count");
+  return many_impl(pool, true, layer_begin, layer_count, d_ids, d_seg_prefix, num_segs, n_total, d_packed,
+                   packed_bytes, stream);
+}
+
+int emm_scatter_many_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const int32_t *d_ids,
+                            const uint32_t *d_seg_prefix, int32_t num_segs, int32_t n_total,
+                            const void *d_packed, uint64_t packed_bytes, void *stream) {
+  if (layer_count < 0) return fail(EMM_ERR_BAD_ARG, "scatter_many_layers: negative layer count");
+  return many_impl(pool, false, layer_begin, layer_count, d_ids, d_seg_prefix, num_segs, n_total, d_packed,
+                   packed_bytes, stream);
 }
 
 int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
@@ -877,15 +915,34 @@ int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
   return rc ? rc : rc2;
 }
 
-static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const void *d_key,
-                       const void *d_value, int64_t kls, int64_t kts, int64_t vls, int64_t vts,
-                       const int64_t *d_slots, int32_t T, void *stream) {
+int emm_upload_ids(emm_ctx *ctx, const int64_t *h_values, int32_t n, int32_t *d_out, void *stream) {
+  if (!ctx) return fail(EMM_ERR_BAD_ARG, "upload_ids: null context");
+  if (n < 0) return fail(EMM_ERR_BAD_ARG, "upload_ids: negative count");
+  if (n == 0) return EMM_OK;
+  if (!h_values || !d_out) return fail(EMM_ERR_BAD_ARG, "upload_ids: null pointer");
+  for (int32_t i = 0; i < n; ++i)
+    if (h_values[i] < 0 || h_values[i] > 0x7fffffffll)
+      return fail(EMM_ERR_ID_RANGE, "upload_ids: value %lld at position %d does not fit a non-negative int32",
+                  (long long)h_values[i], i);
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  IdSlot *s = nullptr;
+  if (int rc = acquire_slot(ctx, (size_t)n, &s)) return rc;
+  for (int32_t i = 0; i < n; ++i) s->h[i] = (int32_t)h_values[i];
+  EMM_CUDA(cudaMemcpyAsync(d_out, s->h, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return finish_slot(s, (cudaStream_t)stream);
+}
+
+// Validates an append and fills the kernel arguments; *align_out receives the common
+// power-of-two alignment of every address and stride involved.
+static int append_prepare(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const void *d_key,
+                          const void *d_value, int64_t kls, int64_t kts, int64_t vls, int64_t vts,
+                          const int64_t *d_slots, int32_t T, emm::AppendArgs *out, uint32_t *align_out) {
   if (!pool) return fail(EMM_ERR_BAD_ARG, "append: null pool");
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
   if (pool->planes != 2) return fail(EMM_ERR_BAD_ARG, "append: needs a KV pool (two planes)");
   if (T < 0) return fail(EMM_ERR_BAD_ARG, "append: negative token count");
-  if (T == 0 || layer_count == 0) return EMM_OK;
-  if (!d_key || !d_value || !d_slots) return fail(EMM_ERR_BAD_ARG, "append: null pointer");
+  if (T > 0 && layer_count > 0 && (!d_key || !d_value || !d_slots)) return fail(EMM_ERR_BAD_ARG, "append: null pointer");
   const emm_pool_desc &d = pool->desc;
   const int64_t head_bytes = (int64_t)d.head_size * d.elem_size;
   const int64_t row_bytes = head_bytes * d.num_kv_heads;
@@ -893,9 +950,6 @@ static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
     return fail(EMM_ERR_BAD_ARG, "append: token stride smaller than a token row (%lld bytes)", (long long)row_bytes);
   if (layer_count > 1 && (kls < (int64_t)T * row_bytes || vls < (int64_t)T * row_bytes))
     return fail(EMM_ERR_BAD_ARG, "append: layer stride smaller than one layer of rows");
-  emm_ctx *ctx = pool->ctx;
-  DeviceGuard guard(ctx->device);
-  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
 
   uint32_t align = pow2_align((uint64_t)head_bytes);
   for (int l = 0; l < d.num_layers; ++l) align = std::min(align, pow2_align(pool->h_layers[l]));
@@ -905,8 +959,10 @@ static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
                             layer_count > 1 ? (uint64_t)kls : 0, layer_count > 1 ? (uint64_t)vls : 0};
   for (uint64_t v : parts) align = std::min(align, pow2_align(v));
   if (align < (uint32_t)d.elem_size) return fail(EMM_ERR_ALIGN, "append: key/value not aligned to elem_size");
+  if ((uint64_t)layer_count * (uint64_t)T * 2ull > 0x3fffffffull)
+    return fail(EMM_ERR_TOO_LARGE, "append: %d layers x %d tokens", layer_count, T);
 
-  emm::AppendArgs a;
+  emm::AppendArgs &a = *out;
   a.layers = pool->d_layers;
   a.plane_stride = (uint64_t)d.plane_stride;
   a.block_stride = (uint64_t)d.block_stride;
@@ -926,14 +982,17 @@ static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
   a.value_layer_stride = (uint64_t)vls;
   a.value_token_stride = (uint64_t)vts;
   a.slots = d_slots;
-  a.status = ctx->d_status;
+  a.status = pool->ctx->d_status;
+  *align_out = align;
+  return EMM_OK;
+}
 
-  const uint64_t rows = (uint64_t)layer_count * (uint64_t)T * 2ull;
-  const uint64_t grid64 = (rows + emm::kAppendWarps - 1) / emm::kAppendWarps;
-  if (grid64 > 0x7fffffffull) return fail(EMM_ERR_TOO_LARGE, "append: %llu rows", (unsigned long long)rows);
-  const int grid = (int)grid64;
+// Launches append_rows for prepared arguments. Call with the context's device current.
+static int append_launch(emm_ctx *ctx, const emm::AppendArgs &a, uint32_t align, cudaStream_t st) {
+  if (a.num_tokens == 0 || a.layer_count == 0) return EMM_OK;
+  const uint64_t rows = (uint64_t)a.layer_count * (uint64_t)a.num_tokens * 2ull;
+  const int grid = (int)((rows + emm::kAppendWarps - 1) / emm::kAppendWarps);
   const int block = emm::kAppendWarps * 32;
-  cudaStream_t st = (cudaStream_t)stream;
   if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
   else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
   else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
@@ -942,6 +1001,19 @@ static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count,
   EMM_CUDA(cudaGetLastError());
   ctx->launches += 1;
   return EMM_OK;
+}
+
+static int append_impl(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const void *d_key,
+                       const void *d_value, int64_t kls, int64_t kts, int64_t vls, int64_t vts,
+                       const int64_t *d_slots, int32_t T, void *stream) {
+  emm::AppendArgs a;
+  uint32_t align = 1;
+  if (int rc = append_prepare(pool, layer_begin, layer_count, d_key, d_value, kls, kts, vls, vts, d_slots, T, &a,
+                              &align))
+    return rc;
+  DeviceGuard guard(pool->ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", pool->ctx->device);
+  return append_launch(pool->ctx, a, align, (cudaStream_t)stream);
 }
 
 int emm_append(emm_pool *pool, int32_t layer, const void *d_key, const void *d_value,
@@ -959,6 +1031,67 @@ int emm_append_all_layers(emm_pool *pool, const void *d_key, const void *d_value
   return append_impl(pool, 0, pool->desc.num_layers, d_key, d_value, key_layer_stride,
                      key_token_stride, value_layer_stride, value_token_stride, d_slot_mapping,
                      num_tokens, stream);
+}
+
+}  // extern "C"
+
+// A per-layer append over static buffers, validated once: what a decode loop that refills the
+// same key/value/slot buffers every step calls once per layer.
+struct emm_append_binding {
+  emm_pool *pool = nullptr;
+  emm::AppendArgs args{};   // layer 0, one layer; the launch fills in the layer
+  uint32_t align = 1;
+  uint64_t key0 = 0, value0 = 0, key_layer_stride = 0, value_layer_stride = 0;
+  int32_t num_layers = 0;
+};
+
+extern "C" {
+
+int emm_append_bind(emm_pool *pool, const void *d_key, const void *d_value, int64_t key_layer_stride,
+                    int64_t key_token_stride, int64_t value_layer_stride, int64_t value_token_stride,
+                    const int64_t *d_slot_mapping, int32_t num_tokens, emm_append_binding **out) {
+  if (!out) return fail(EMM_ERR_BAD_ARG, "append_bind: null out");
+  *out = nullptr;
+  if (!pool) return fail(EMM_ERR_BAD_ARG, "append_bind: null pool");
+  emm_append_binding *b = new (std::nothrow) emm_append_binding();
+  if (!b) return fail(EMM_ERR_NOMEM, "append_bind: host allocation failed");
+  // Validated as the all-layers call (every layer's rows must exist), launched one layer at a time.
+  if (int rc = append_prepare(pool, 0, pool->desc.num_layers, d_key, d_value, key_layer_stride, key_token_stride,
+                              value_layer_stride, value_token_stride, d_slot_mapping, num_tokens, &b->args,
+                              &b->align)) {
+    delete b;
+    return rc;
+  }
+  b->pool = pool;
+  b->key0 = (uint64_t)d_key;
+  b->value0 = (uint64_t)d_value;
+  b->key_layer_stride = (uint64_t)key_layer_stride;
+  b->value_layer_stride = (uint64_t)value_layer_stride;
+  b->num_layers = pool->desc.num_layers;
+  b->args.layer_count = 1;
+  b->args.key_layer_stride = 0;
+  b->args.value_layer_stride = 0;
+  *out = b;
+  return EMM_OK;
+}
+
+int emm_append_bound(emm_append_binding *b, int32_t layer, void *stream) {
+  if (!b) return fail(EMM_ERR_BAD_ARG, "append_bound: null binding");
+  if (layer < 0 || layer >= b->num_layers)
+    return fail(EMM_ERR_BAD_ARG, "append_bound: layer %d outside [0, %d)", layer, b->num_layers);
+  emm_ctx *ctx = b->pool->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
+  emm::AppendArgs a = b->args;
+  a.layer_begin = (uint32_t)layer;
+  a.key = b->key0 + (uint64_t)layer * b->key_layer_stride;
+  a.value = b->value0 + (uint64_t)layer * b->value_layer_stride;
+  return append_launch(ctx, a, b->align, (cudaStream_t)stream);
+}
+
+int emm_append_unbind(emm_append_binding *b) {
+  delete b;
+  return EMM_OK;
 }
 
 int emm_compact_plan(const int64_t *table_ids, int64_t n_ids, int64_t num_blocks,
@@ -1327,27 +1460,36 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaStatusBytes 
 
 constexpr int kNaMaxDevices = 64;
 struct NoAllocDevice {
-  bool ready = false;
+  std::once_flag once;
+  int setup_rc = EMM_OK;
+  std::string setup_error;
   unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on this device
   int sm_count = 0;
   int max_smem_optin = 0;
 };
 NoAllocDevice g_noalloc_dev[kNaMaxDevices];
 
-// Once per device, with that device current. In host code the array's name is
-// only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
+// Once per device (threads racing on the first call are serialised), with that
+// device current. In host code the array's name is only a handle; the address
+// a kernel can use comes from cudaGetSymbolAddress.
 int noalloc_setup(int device, NoAllocDevice **out) {
   if (device < 0 || device >= kNaMaxDevices)
     return fail(EMM_ERR_BAD_ARG, "gather_noalloc: device %d outside [0, %d)", device, kNaMaxDevices);
   NoAllocDevice &d = g_noalloc_dev[device];
-  if (!d.ready) {
+  std::call_once(d.once, [&d, device] {
     void *ptr = nullptr;
-    EMM_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-    EMM_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
-    EMM_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess)
+      e = cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e != cudaSuccess) {
+      d.setup_rc = EMM_ERR_CUDA;
+      d.setup_error = std::string("gather_noalloc: set-up on device failed: ") + cudaGetErrorString(e);
+      return;
+    }
     d.scratch = static_cast<unsigned char *>(ptr);
-    d.ready = true;
-  }
+  });
+  if (d.setup_rc != EMM_OK) return fail(d.setup_rc, "%s", d.setup_error.c_str());
   *out = &d;
   return EMM_OK;
 }
@@ -1384,6 +1526,13 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", device);
   NoAllocDevice *nd = nullptr;
   if (int rc = noalloc_setup(device, &nd)) return rc;
+  // The table and the layer addresses are read from host memory at call time;
+  // a capturing stream would record the copies, not perform them, and a later
+  // replay would read host memory that no longer holds them.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  EMM_CUDA(cudaStreamIsCapturing((cudaStream_t)stream, &capturing));
+  if (capturing != cudaStreamCaptureStatusNone)
+    return fail(EMM_ERR_BAD_ARG, "gather_noalloc: the stream is capturing; this entry uploads its table at call time");
 
   uint32_t align = pow2_align((uint64_t)desc->block_stride);
   if (planes == 2) align = std::min(align, pow2_align((uint64_t)desc->plane_stride));
@@ -1405,7 +1554,8 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   // The array keeps the previous call's contents: the status word must start
   // at zero; the layer array and the table are overwritten up to what is read.
   EMM_CUDA(cudaMemsetAsync(d_status, 0, 16, st));
-  // Pageable sources: the runtime has copied them out before these calls return.
+  // Pageable sources: the runtime has copied them out before these calls return,
+  // which it can only do once earlier work on `st` has finished (the host waits for it).
   EMM_CUDA(cudaMemcpyAsync(d_layers, layer_addr, sizeof(uint64_t) * desc->num_layers, cudaMemcpyHostToDevice, st));
   EMM_CUDA(cudaMemcpyAsync(d_ids, ids32, sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
 
@@ -1427,6 +1577,8 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   a.layer_count = (uint32_t)desc->num_layers;
   a.page_bytes = (uint32_t)page;
   a.status = reinterpret_cast<int *>(d_status);
+  a.wait_limit_ns = emm::kDefaultWaitLimitNs;
+  a.tx_overcount = 0;
 
   if (align >= 16) {
     int64_t chunk = std::min<int64_t>(32768, page);

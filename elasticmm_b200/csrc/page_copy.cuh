@@ -60,6 +60,9 @@ struct PageCopyArgs {
   uint32_t chunks_per_page;  // ceil(page_bytes / chunk_bytes)
   uint64_t total_chunks;     // layer_count * planes * n * chunks_per_page
   int *status;               // [0] = sticky status code, [1..2] = detail (lo, hi)
+  uint64_t wait_limit_ns;    // bulk family: longest a lane waits for one load before it gives up
+  uint32_t tx_overcount;     // bulk family, test hook: bytes added to every expected transaction count
+                             // (0 in every product path; non-zero makes each wait run out)
 };
 
 // Status codes duplicated from emm_kv.h so that device code needs no C header.
@@ -68,7 +71,7 @@ constexpr int kStatusTimeout = 5;
 
 constexpr int kMaxStages = 8;
 constexpr int kMaxWarps = 8;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per bounded wait
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;  // 2 s per bounded wait unless the context says otherwise
 
 struct ChunkAddr {
   uint64_t src;
@@ -192,13 +195,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Waits for the phase with the given parity, for at most kWaitLimitNs.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Waits for the phase with the given parity, for at most limit_ns.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
 }
 
@@ -297,7 +300,7 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
     my_dst[s] = ca.dst;
     my_len[s] = ca.len;
     if (ca.len) {
-      mbar_expect_tx(bar, ca.len);
+      mbar_expect_tx(bar, ca.len + a.tx_overcount);
       if (l2_hint & 1) bulk_load_hint(ring + s * a.chunk_bytes, ca.src, ca.len, bar, policy);
       else bulk_load(ring + s * a.chunk_bytes, ca.src, ca.len, bar);
     } else {
@@ -324,7 +327,7 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
     const ChunkAddr cur_ca = next_ca;
     if (jn + 1 < n_mine) next_ca = decode_chunk<kSeg>(a, stream_id + (jn + 1) * stream_step);
 
-    if (!mbar_wait_bounded(smem_u32(&my_bars[s]), parity)) {
+    if (!mbar_wait_bounded(smem_u32(&my_bars[s]), parity, a.wait_limit_ns)) {
       report(a.status, kStatusTimeout, (long long)(stream_id + j * stream_step));
       timed_out = true;
       break;
@@ -355,7 +358,7 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
     for (uint64_t q = j; q < jn; ++q) {
       const uint32_t qs = (uint32_t)(q % stages);
       const uint32_t qp = (uint32_t)((q / stages) & 1);
-      if (!mbar_wait_bounded(smem_u32(&my_bars[qs]), qp)) break;
+      if (!mbar_wait_bounded(smem_u32(&my_bars[qs]), qp, a.wait_limit_ns)) break;
     }
   }
   bulk_wait_all();  // stores complete (and have left shared memory) before exit

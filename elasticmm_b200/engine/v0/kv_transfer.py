@@ -151,6 +151,13 @@ class V0KVTransferManager:
                     return {"bytes": 0, "blocks": len(src_blocks), "passive": True}
                 if src is not None and src_rank not in dst.peer_pools:
                     dst.attach_local_peer(src_rank, src)      # both workers in this process, two GPUs
+                if src is not None:
+                    # The sink's kernel reads the source GPU's pool: order it after whatever the source
+                    # has queued on its current stream (the reference's send runs on the source's stream
+                    # and is ordered after the prefill kernels in the same way).
+                    ready = torch.cuda.Event()
+                    ready.record(torch.cuda.current_stream(src.device))
+                    torch.cuda.current_stream(dst.device).wait_event(ready)
                 worker, res = dst, dst.p2p_pull_kv(src_rank, src_blocks, dst_blocks)      # sink loads over the link
             else:
                 if src is None:
@@ -284,6 +291,20 @@ class V0KVTransferManager:
         self.last_result = {"bytes": data.numel() * data.element_size(), "blocks": len(src_blocks),
                             "elapsed": time.perf_counter() - start}
         return True
+
+    def transfer_kv_cache_batch(self, transfers: Sequence[Transfer]) -> bool:
+        """Moves several requests at once and returns when all of them have landed: the requests of
+        each (source, sink) pair travel as one merged table (one launch per direction on the copy
+        path). Per-request `transfer_kv_cache` stays synchronous by default, because the reference's
+        engines read the destination blocks right after awaiting it
+        (elasticmm/engine/v0/stage_engine.py:1506-1566); this is the call for a caller that has
+        several requests in hand (the reference's own batching branch,
+        elasticmm/engine/v0/kv_transfer.py:342-418, queues them and was switched off at
+        elasticmm/engine/v0/backend.py:109 because nothing flushed the queue)."""
+        for t in transfers:
+            self._transfer_queue.setdefault((t.src_rank, t.dst_rank), []).append(
+                (t.request_id, list(t.src_blocks), list(t.dst_blocks)))
+        return self.flush()
 
     def transfer_many(self, plan: MigrationPlan) -> bool:
         """Moves a whole plan: one table per (source, sink) pair.

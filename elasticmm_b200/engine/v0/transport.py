@@ -19,7 +19,7 @@ without blocking the host.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 Chunk = Tuple[int, int]  # (layer_begin, layer_count)
 
@@ -222,3 +222,133 @@ class MigrationPlan:
                 if b in used:
                     raise ValueError(f"{t.request_id}: destination block {b} on rank {t.dst_rank} assigned twice")
                 used.add(b)
+
+
+class WaveLedger:
+    """Host-side record of which (wave, source) moves have finished, shared by all ranks.
+
+    A role switch that does not fit the pools moves in waves. The reference has
+    no such record: it awaits every request's RPC before the next
+    (elasticmm/engine/v0/backend.py:674-718) and frees source blocks without
+    waiting for the copy (elasticmm/engine/v0/stage_engine.py:1336). Here every
+    sink posts one completion per (wave, source) once its copy of that source's
+    blocks has finished on the device; a source may reuse a wave's blocks when
+    all of its sinks of that wave have posted, and a sink starts wave w of a
+    source only when wave w - depth of that source is complete everywhere. No
+    rank waits for ranks it does not exchange data with, and nobody meets at a
+    barrier between waves.
+
+    `store` is any torch.distributed key-value store (TCPStore, FileStore,
+    HashStore, PrefixStore); counters live under `prefix`, which must be unique
+    per migration (epoch) because counters are never reset.
+    """
+
+    def __init__(self, store, prefix: str, poll_s: float = 20e-6, timeout_s: float = 30.0):
+        self.store = store
+        self.prefix = prefix
+        self.poll_s = poll_s
+        self.timeout_s = timeout_s
+
+    def _key(self, wave: int, source: int) -> str:
+        return f"{self.prefix}/w{wave}/s{source}"
+
+    def post(self, wave: int, source: int) -> int:
+        """This sink's copy of `source`'s blocks of `wave` has finished; returns the new count."""
+        return int(self.store.add(self._key(wave, source), 1))
+
+    def count(self, wave: int, source: int) -> int:
+        return int(self.store.add(self._key(wave, source), 0))
+
+    def failed(self) -> Optional[str]:
+        if int(self.store.add(f"{self.prefix}/failed_flag", 0)):
+            return self.store.get(f"{self.prefix}/failed").decode("utf-8", "replace")
+        return None
+
+    def mark_failed(self, reason: str) -> None:
+        """Marks the migration as failed so that ranks waiting in wait() stop waiting."""
+        self.store.set(f"{self.prefix}/failed", reason.encode("utf-8", "replace")[:200])
+        self.store.add(f"{self.prefix}/failed_flag", 1)
+
+    def wait(self, wave: int, source: int, expected: int) -> None:
+        """Returns once `expected` sinks have posted (wave, source); raises TimeoutError after
+        `timeout_s`, RuntimeError if another rank marked the migration as failed."""
+        if expected <= 0:
+            return
+        import time
+
+        deadline = time.monotonic() + self.timeout_s
+        spins, pause = 0, self.poll_s
+        while self.count(wave, source) < expected:
+            spins += 1
+            if spins % 16 == 0:
+                why = self.failed()
+                if why is not None:
+                    raise RuntimeError(f"migration failed on another rank: {why}")
+            if time.monotonic() > deadline:
+                raise TimeoutError(f"wave {wave} of source {source}: {self.count(wave, source)} of {expected} "
+                                   f"sinks finished within {self.timeout_s} s")
+            if pause:
+                time.sleep(pause)
+                pause = min(pause * 2, 500e-6)  # a long wait polls the store gently
+
+
+def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, depth: int,
+              launch: Callable[[int, int, List[object]], object],
+              wait_done: Callable[[object], float],
+              on_wave_landed: Optional[Callable[[int], None]] = None) -> List[float]:
+    """Drives one rank through a sequence of waves without a barrier between waves.
+
+    Sink side. For wave w and each of its sources (in the plan's pull order):
+    wait until all sinks have posted wave w - depth of that source, then
+    `launch(w, source, earlier)` starts this sink's copy of that source's blocks,
+    ordered after the handles in `earlier` (this sink's own copies of wave
+    w - depth, whose destination blocks wave w may reuse); it returns a handle.
+    After wave w has been launched, the waves up to w - depth + 1 are completed:
+    `wait_done(handle)` blocks until a copy has finished and returns its
+    duration in ms, `on_wave_landed` runs, and the wave is posted in the ledger.
+    So with depth 2 a sink always has the next wave queued behind the running
+    one, and runs at most `depth` waves ahead of the slowest sink that shares a
+    source with it; depth 1 degenerates to one wave at a time.
+
+    Source side. A source returns once every one of its waves is complete
+    everywhere: from then on all the blocks it offered may be freed.
+
+    Returns this rank's per-wave durations (the longest copy of each wave; empty
+    for a rank that receives nothing).
+    """
+    if depth < 1:
+        raise ValueError("depth must be at least 1")
+    launched: List[List[Tuple[int, object]]] = []
+    wave_ms: List[float] = []
+    finished = 0  # waves [0, finished) of this rank are complete and posted
+
+    def finish(w: int) -> None:
+        longest = 0.0
+        for _, handle in launched[w]:
+            longest = max(longest, float(wait_done(handle)))
+        if on_wave_landed is not None:
+            on_wave_landed(w)
+        for source, _ in launched[w]:
+            ledger.post(w, source)
+        if launched[w]:
+            wave_ms.append(longest)
+
+    for w, plan in enumerate(plans):
+        this_wave: List[Tuple[int, object]] = []
+        earlier = [h for _, h in launched[w - depth]] if w >= depth else []
+        for source in plan.pull_order(rank):
+            if w >= depth:
+                ledger.wait(w - depth, source, len(plans[w - depth].outgoing(source)))
+            this_wave.append((source, launch(w, source, earlier)))
+        launched.append(this_wave)
+        while finished <= w - depth + 1:  # keep at most `depth` waves of this rank unposted
+            finish(finished)
+            finished += 1
+    while finished < len(plans):
+        finish(finished)
+        finished += 1
+    for w, plan in enumerate(plans):
+        n = len(plan.outgoing(rank))
+        if n:
+            ledger.wait(w, rank, n)
+    return wave_ms

@@ -21,9 +21,11 @@ import torch
 import torch.distributed as dist
 
 from ... import _lib
-from ...kv_pool import Context, KVPool, get_context
+from ...kv_pool import Context, KVPool, _as_host_ids, get_context
 from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_recv,
-                        pipelined_send, PIPELINE_DEPTH)
+                        pipelined_send, run_waves, PIPELINE_DEPTH)
+
+ALLTOALL_MESSAGE_BYTES = 256 << 20  # target bytes a rank packs per chunk of the all-to-all migration
 from .utils import EngineStage
 
 import contextlib
@@ -372,7 +374,7 @@ class V0Worker:
             n = len(block_indices)
             if n == 0:
                 return {"bytes": 0, "blocks": 0}
-            ids = pool.upload_ids(pool._validated(_lib_ids(block_indices), unique=not sending))
+            ids = pool.upload_ids(pool._validated(_as_host_ids(block_indices), unique=not sending))
             chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
             slots = self._staging_views(pool, n, chunks)
             with _range(f"emm.p2p_{what}_kv"):
@@ -566,47 +568,128 @@ class V0Worker:
         return {"bytes": len(src_blocks) * pool.block_bytes(), "blocks": len(src_blocks)}
 
     # -- plan-level migration -----------------------------------------------------
+    def _agree(self, error: Optional[str]) -> Optional[str]:
+        """Collective over the process group: None if no rank reports an error, else this
+        rank's own message or a note that a peer failed. Every rank of a migration passes
+        through the same _agree calls, so a rank that fails a host-side check never leaves the
+        others waiting in an exchange or at the exit (they all return an error together)."""
+        backend = dist.get_backend(self.process_group)
+        flag = torch.tensor([1 if error else 0], dtype=torch.int32,
+                            device=self.device if backend == "nccl" else "cpu")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.process_group)
+        if int(flag.item()) == 0:
+            return None
+        return error or "another rank of the migration reported an error; nothing was moved by this rank"
+
+    def _own_stream_sync(self) -> None:
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def _device_error(self, what: str) -> Optional[str]:
+        """Waits for this GPU and reads the sticky device status word."""
+        torch.cuda.synchronize(self.device)
+        rc, _ = self.ctx.status()
+        return None if rc == _lib.OK else f"{what} failed on device: {_lib.last_error()}"
+
+    def _check_plan_part(self, plan: MigrationPlan, method: str) -> Optional[str]:
+        """Host-side validation of this rank's part of a plan, before anything is launched."""
+        rank = self.get_global_rank()
+        pool = self.pool
+        if pool is None:
+            return "KV cache not initialized"
+        try:
+            for peer in plan.incoming(rank):
+                src_ids, dst_ids = plan.tables_np(peer, rank)
+                pool._validated(dst_ids, unique=False)
+                if method == "pull" and peer not in self.peer_pools:
+                    return f"pool of rank {peer} is not mapped"
+                if method == "pull":
+                    self.peer_pools[peer]._validated(src_ids)
+            incoming = [plan.tables_np(peer, rank)[1] for peer in plan.incoming(rank)]
+            if incoming:
+                import numpy as np
+
+                pool._validated(np.concatenate(incoming), unique=True)
+            for peer in plan.outgoing(rank):
+                src_ids, dst_ids = plan.tables_np(rank, peer)
+                pool._validated(src_ids)
+                if method == "push" and peer not in self.peer_pools:
+                    return f"pool of rank {peer} is not mapped"
+                if method == "push":
+                    self.peer_pools[peer]._validated(dst_ids, unique=True)
+        except _lib.EmmError as e:
+            return str(e)
+        if method == "alltoall" and self._nccl_comm is None:
+            return "alltoall migration needs init_native_nccl()"
+        if method == "nccl" and plan.outgoing(rank) and plan.incoming(rank):
+            return ("nccl migration needs each rank to be a pure source or a pure sink; "
+                    "use the peer method for exchanges")
+        return None
+
+    def _pull_all(self, plan: MigrationPlan, tables: Optional[Dict[int, Tuple[Any, Any]]] = None):
+        """Launches this sink's pulls of one wave, all sources side by side on one stream each, with the
+        grids capped so that the launches together hold at most one CTA per SM: measured on NVSwitch, two
+        full-size pull kernels side by side halve the rate, two half-size ones run at full link speed, and
+        a flow that is left alone still saturates the link with its share of CTAs. Returns
+        (error or None, blocks, [(peer, stream)])."""
+        rank = self.get_global_rank()
+        peers = plan.pull_order(rank)
+        cap = max(24, self.ctx.sm_count // max(1, len(peers))) if len(peers) > 1 else None
+        main = torch.cuda.current_stream(self.device)
+        used, moved = [], 0
+        for peer in peers:
+            src_ids, dst_ids = tables[peer] if tables is not None else plan.tables_np(peer, rank)
+            stream = self._peer_streams.get(peer)
+            if stream is None:
+                stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                res = self.p2p_pull_kv(peer, src_ids, dst_ids, max_ctas=cap)
+            used.append((peer, stream))
+            if "error" in res:
+                return res["error"], moved, used
+            moved += res["blocks"]
+        return None, moved, used
+
     def migrate(self, plan: MigrationPlan, method: str = "pull") -> Dict[str, Any]:
-        """Runs this rank's part of a migration plan; every rank in the plan calls it.
+        """Runs this rank's part of a migration plan; every rank of the process group calls it.
 
         method "pull" (default; "peer" is an alias): each sink launches one
-        direct-load kernel per source, side by side with capped grids, then all
-        ranks meet at a barrier. method "push": each source launches one
-        direct-store kernel per sink instead, one sink at a time. method "alltoall":
-        per layer chunk, one gather for all sinks, one grouped NCCL exchange with every
-        peer, one scatter for all sources, pipelined over the chunks (needs
-        init_native_nccl). method "nccl": per pair, the staged pipeline of
-        p2p_send_kv / p2p_recv_kv; every rank walks the pairs in the plan's one
-        global order (sources start at different sinks), which rules out a
-        circular wait.
+        direct-load kernel per source, side by side with capped grids. method
+        "push": each source launches one direct-store kernel per sink instead,
+        one sink at a time. method "alltoall": per layer chunk, one gather for all
+        sinks, one grouped NCCL exchange with one message per peer, one scatter for
+        all sources, pipelined over the chunks (needs init_native_nccl). method
+        "nccl": per pair, the staged pipeline of p2p_send_kv / p2p_recv_kv; every
+        rank walks the pairs in the plan's one global order (sources start at
+        different sinks), which rules out a circular wait.
+
+        Ordering. A source's blocks must be final on the source's CURRENT stream
+        when it calls migrate: the source waits for that stream before the entry
+        agreement, and no sink reads before the agreement has completed. The call
+        returns after every rank's copies have finished (the exit agreement), so a
+        source may free or overwrite its blocks as soon as migrate returns.
+
+        Errors. Host-side checks run first and all ranks agree on their outcome
+        before anything is launched; device-side status is agreed on at the exit.
+        If any rank fails, every rank returns {"error": ...} and none hangs.
         """
-        rank = self.get_global_rank()
-        pool = self._require_pool()
-        moved = 0
         if method == "peer":
             method = "pull"
+        if method not in ("pull", "push", "alltoall", "nccl"):
+            raise ValueError(f"unknown migration method {method!r}")
+        rank = self.get_global_rank()
+        error = self._check_plan_part(plan, method)
+        if plan.outgoing(rank):
+            self._own_stream_sync()  # what this source wrote is visible to its sinks
+        error = self._agree(error)
+        if error:
+            return {"error": error, "bytes": 0, "blocks": 0}
+        pool = self._require_pool()
+        moved = 0
         if method == "pull":
-            # A sink pulls from all its sources at once, one stream per source, with the grids capped
-            # so that the launches together hold at most one CTA per SM: measured on NVSwitch, two
-            # full-size pull kernels side by side halve the rate, two half-size ones run at full link
-            # speed, and a flow that is left alone still saturates the link with its share of CTAs.
-            peers = plan.pull_order(rank)
-            cap = max(24, self.ctx.sm_count // max(1, len(peers)))
+            error, moved, used = self._pull_all(plan)
             main = torch.cuda.current_stream(self.device)
-            used = []
-            for peer in peers:
-                src_ids, dst_ids = plan.tables_np(peer, rank)
-                stream = self._peer_streams.get(peer)
-                if stream is None:
-                    stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
-                stream.wait_stream(main)
-                with torch.cuda.stream(stream):
-                    res = self.p2p_pull_kv(peer, src_ids, dst_ids, max_ctas=cap if len(peers) > 1 else None)
-                used.append(stream)
-                if "error" in res:
-                    return res
-                moved += res["blocks"]
-            for stream in used:
+            for _, stream in used:
                 main.wait_stream(stream)
         elif method == "push":
             # A source pushes to one sink at a time, sources starting at different sinks.
@@ -614,20 +697,12 @@ class V0Worker:
                 src_ids, dst_ids = plan.tables_np(rank, peer)
                 res = self.p2p_push_kv(peer, src_ids, dst_ids)
                 if "error" in res:
-                    return res
+                    error = res["error"]
+                    break
                 moved += res["blocks"]
-        if method in ("pull", "push"):
-            torch.cuda.synchronize(self.device)
-            rc, _ = self.ctx.status()
-            dist.barrier(group=self.process_group)
-            if rc != _lib.OK:
-                return {"error": f"{method} failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
         elif method == "alltoall":
-            return self._migrate_alltoall(plan)
-        elif method == "nccl":
-            if plan.outgoing(rank) and plan.incoming(rank):
-                return {"error": "nccl migration needs each rank to be a pure source or a pure sink; "
-                                 "use the peer method for exchanges", "bytes": 0, "blocks": 0}
+            moved = self._migrate_alltoall(plan)
+        else:
             for src, dst in plan.ordered_pairs():
                 if src == rank:
                     res = self.p2p_send_kv(dst, plan.tables(src, dst)[0])
@@ -636,140 +711,181 @@ class V0Worker:
                 else:
                     continue
                 if "error" in res:
-                    return res
-                moved += res["blocks"]
-        else:
-            raise ValueError(f"unknown migration method {method!r}")
+                    error = error or res["error"]  # keep walking the pairs: the peers are in their halves
+                else:
+                    moved += res["blocks"]
+        if not error:
+            error = self._device_error(method)
+        error = self._agree(error)  # also the exit meeting point: every copy of the plan has landed
+        if error:
+            return {"error": error, "bytes": 0, "blocks": 0}
         return {"bytes": moved * pool.block_bytes(), "blocks": moved}
 
+    def migrate_waves(self, plans: Sequence[MigrationPlan], ledger, depth: int = 2,
+                      tables: Optional[Sequence[Dict[int, Tuple[Any, Any]]]] = None,
+                      on_wave_landed=None) -> Dict[str, Any]:
+        """Moves a sequence of waves by direct loads with no barrier between waves.
 
-def _migrate_alltoall(self, plan: MigrationPlan) -> Dict[str, Any]:
-    """Per-layer pipelined all-to-all of packed pages over the library's NCCL communicator.
+        `plans[w]` is wave w; every rank of the process group makes the call with the
+        same list. Blocks (on a source and on a sink) may be used again by wave
+        w + depth: a sink launches its pull of wave w from a source only after all
+        sinks have posted wave w - depth of that source in `ledger` (a WaveLedger
+        over a store all ranks share), and it orders wave w on its own device after
+        its wave w - depth. A sink therefore runs up to `depth` waves ahead of the
+        slowest sink, and a source's link stays busy while one sink is still
+        finishing. A source returns when all of its waves are complete, which is its
+        signal that every block it offered may be freed.
 
-    Every rank of the plan calls this. For each chunk of layers a source packs the blocks of all
-    its sinks with one gather (tables concatenated in sink order, so each sink's pages of one
-    layer and plane are one contiguous segment), all ranks run one grouped exchange in which a
-    source sends those segments and a sink receives the segments of all its sources into one
-    staging buffer, and the sink unpacks them with one scatter over its concatenated destination
-    table. Packing chunk c+1, exchanging chunk c and unpacking chunk c-1 overlap on three streams
-    with two staging slots per direction. A rank may be source and sink at once: its sends and
-    receives of a chunk share one NCCL group.
-    """
-    if self._nccl_comm is None:
-        return {"error": "alltoall migration needs init_native_nccl()", "bytes": 0, "blocks": 0}
-    rank = self.get_global_rank()
-    pool = self._require_pool()
-    page = pool.page_bytes
-    sinks = sorted(plan.outgoing(rank))
-    sources = sorted(plan.incoming(rank))
-    out_tabs = [plan.tables_np(rank, d)[0] for d in sinks]
-    in_tabs = [plan.tables_np(s, rank)[1] for s in sources]
-    n_out = [len(t) for t in out_tabs]
-    n_in = [len(t) for t in in_tabs]
-    N_out, N_in = sum(n_out), sum(n_in)
-    # one chunk schedule for everybody: sized by the busiest rank of the plan
-    totals: Dict[int, int] = {}
-    for t in plan.transfers:
-        totals[("o", t.src_rank)] = totals.get(("o", t.src_rank), 0) + len(t.src_blocks)
-        totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
-    n_ref = max(totals.values()) if totals else 0
-    chunks = plan_chunks(pool.num_layers, n_ref, page)
-    if not chunks:
-        dist.barrier(group=self.process_group)
-        return {"bytes": 0, "blocks": 0}
-    lc_max = max_chunk_layers(chunks)
-    import numpy as np
+        `tables[w][source]` optionally gives device-resident (src ids, dst ids) int32
+        tensors for this sink; otherwise the plan's host lists are uploaded.
+        `on_wave_landed(w)` is called on a sink after its copies of wave w have
+        finished and before it posts the wave (a verification hook).
 
-    ctx = self.ctx
-    main = torch.cuda.current_stream(self.device)
-    if self._a2a is None:
-        self._a2a = {"pack": torch.cuda.Stream(self.device), "wire": torch.cuda.Stream(self.device),
-                     "unpack": torch.cuda.Stream(self.device), "out": None, "in": None}
-    a2a = self._a2a
-    need_out = 2 * pool.packed_bytes(N_out, lc_max)
-    need_in = 2 * pool.packed_bytes(N_in, lc_max)
-    if N_out and (a2a["out"] is None or a2a["out"].numel() < need_out):
-        a2a["out"] = torch.empty(need_out, dtype=torch.uint8, device=self.device)
-    if N_in and (a2a["in"] is None or a2a["in"].numel() < need_in):
-        a2a["in"] = torch.empty(need_in, dtype=torch.uint8, device=self.device)
-    ids_out = pool.upload_ids(pool._validated(np.concatenate(out_tabs))) if N_out else None
-    ids_in = pool.upload_ids(pool._validated(np.concatenate(in_tabs), unique=True)) if N_in else None
-    for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
-        st.wait_stream(main)
-    ev_packed = [torch.cuda.Event(), torch.cuda.Event()]
-    ev_wired = [torch.cuda.Event(), torch.cuda.Event()]
-    ev_unpacked = [torch.cuda.Event(), torch.cuda.Event()]
+        Returns {"bytes", "blocks", "wave_ms"} with this sink's device time per wave,
+        or {"error": ...} on every rank if any rank failed.
+        """
+        rank = self.get_global_rank()
+        pool = self.pool
+        error = None
+        for plan in plans:
+            error = error or self._check_plan_part(plan, "pull")
+        if any(plan.outgoing(rank) for plan in plans):
+            self._own_stream_sync()
+        error = self._agree(error)
+        if error:
+            return {"error": error, "bytes": 0, "blocks": 0}
+        moved, wave_ms = [0], []
+        try:
+            def launch(w: int, peer: int, earlier):
+                plan = plans[w]
+                cap = max(24, self.ctx.sm_count // max(1, len(plan.incoming(rank)))) if len(plan.incoming(rank)) > 1 else None
+                src_ids, dst_ids = tables[w][peer] if tables is not None else plan.tables_np(peer, rank)
+                stream = self._peer_streams.get(peer)
+                if stream is None:
+                    stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
+                if w == 0:
+                    stream.wait_stream(torch.cuda.current_stream(self.device))
+                for _, done in earlier:  # this sink's copies of wave w - depth, from any source, are done
+                    stream.wait_event(done)
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(stream):
+                    ev0.record(stream)
+                    res = self.p2p_pull_kv(peer, src_ids, dst_ids, max_ctas=cap)
+                    ev1.record(stream)
+                if "error" in res:
+                    raise RuntimeError(res["error"])
+                moved[0] += res["blocks"]
+                return ev0, ev1
 
-    n_sinks_of = {s: len(plan.outgoing(s)) for s, _ in plan.pairs()}
-    n_sources_of = {d: len(plan.incoming(d)) for _, d in plan.pairs()}
+            def wait_done(handle) -> float:
+                handle[1].synchronize()
+                return handle[0].elapsed_time(handle[1])
 
-    def whole_chunk(src: int, dst: int) -> bool:
-        """Both ends see this pair's pages of a chunk as one contiguous run (the source has no other
-        sink, the sink no other source), so the chunk travels as one message instead of one per
-        layer and plane. Decided from the plan alone, hence identically on both ends."""
-        return n_sinks_of[src] == 1 and n_sources_of[dst] == 1
+            wave_ms = run_waves(plans, rank, ledger, depth, launch, wait_done, on_wave_landed)
+            main = torch.cuda.current_stream(self.device)
+            for stream in self._peer_streams.values():
+                main.wait_stream(stream)
+        except Exception as e:  # reported, not raised; the others stop waiting through the ledger
+            error = f"{type(e).__name__}: {e}"
+            try:
+                ledger.mark_failed(error)
+            except Exception:
+                pass
+        if not error:
+            error = self._device_error("pull")
+        error = self._agree(error)
+        if error:
+            return {"error": error, "bytes": 0, "blocks": 0}
+        return {"bytes": moved[0] * pool.block_bytes(), "blocks": moved[0], "wave_ms": wave_ms}
 
-    def slot_view(buf, slot, n_total, lc):
-        nbytes = pool.packed_bytes(n_total, lc)
-        half = buf.numel() // 2
-        flat = buf[slot * half: slot * half + nbytes]
-        return flat, pool._logical(flat.view(pool.dtype).view(pool.packed_shape(n_total, lc)))
+    def _migrate_alltoall(self, plan: MigrationPlan) -> int:
+        """Per-layer pipelined all-to-all of packed pages over the library's NCCL communicator; returns
+        the number of blocks this rank sent and received.
 
-    with _range("emm.migrate_alltoall"):
-        for c, (begin, count) in enumerate(chunks):
-            slot = c & 1
-            ops = []
-            if N_out:
-                flat_out, view_out = slot_view(a2a["out"], slot, N_out, count)
-                with torch.cuda.stream(a2a["pack"]):
+        For each chunk of layers a source packs the blocks of all its sinks with one gather laid out
+        [sink][layer][plane][n_sink][page], so that each sink's share of the chunk is ONE contiguous
+        message; all ranks run one grouped exchange (one ncclSend per sink, one ncclRecv per source);
+        a sink unpacks [source][layer][plane][n_source][page] with one scatter. Packing chunk c+1,
+        exchanging chunk c and unpacking chunk c-1 overlap on three streams with two staging slots
+        per direction. A rank may be source and sink at once: its sends and receives of a chunk
+        share one NCCL group.
+        """
+        rank = self.get_global_rank()
+        pool = self._require_pool()
+        page = pool.page_bytes
+        sinks = sorted(plan.outgoing(rank))
+        sources = sorted(plan.incoming(rank))
+        n_out = [len(plan.tables_np(rank, d)[0]) for d in sinks]
+        n_in = [len(plan.tables_np(s, rank)[1]) for s in sources]
+        N_out, N_in = sum(n_out), sum(n_in)
+        # one chunk schedule for everybody: sized by the busiest rank of the plan
+        totals: Dict[Tuple[str, int], int] = {}
+        for t in plan.transfers:
+            totals[("o", t.src_rank)] = totals.get(("o", t.src_rank), 0) + len(t.src_blocks)
+            totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
+        n_ref = max(totals.values()) if totals else 0
+        chunks = plan_chunks(pool.num_layers, n_ref, page, target_bytes=ALLTOALL_MESSAGE_BYTES)
+        if not chunks:
+            return 0
+        lc_max = max_chunk_layers(chunks)
+
+        ctx = self.ctx
+        main = torch.cuda.current_stream(self.device)
+        if self._a2a is None:
+            self._a2a = {"pack": torch.cuda.Stream(self.device), "wire": torch.cuda.Stream(self.device),
+                         "unpack": torch.cuda.Stream(self.device), "out": None, "in": None}
+        a2a = self._a2a
+        need_out = 2 * pool.packed_bytes(N_out, lc_max)
+        need_in = 2 * pool.packed_bytes(N_in, lc_max)
+        if N_out and (a2a["out"] is None or a2a["out"].numel() < need_out):
+            a2a["out"] = torch.empty(need_out, dtype=torch.uint8, device=self.device)
+        if N_in and (a2a["in"] is None or a2a["in"].numel() < need_in):
+            a2a["in"] = torch.empty(need_in, dtype=torch.uint8, device=self.device)
+        tab_out = pool.many_tables([plan.tables_np(rank, d)[0] for d in sinks]) if N_out else None
+        tab_in = pool.many_tables([plan.tables_np(s, rank)[1] for s in sources], unique=True) if N_in else None
+        for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
+            st.wait_stream(main)
+        ev_packed = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_wired = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_unpacked = [torch.cuda.Event(), torch.cuda.Event()]
+
+        def slot_of(buf: torch.Tensor, slot: int) -> torch.Tensor:
+            half = buf.numel() // 2
+            return buf[slot * half:(slot + 1) * half]
+
+        with _range("emm.migrate_alltoall"):
+            for c, (begin, count) in enumerate(chunks):
+                slot = c & 1
+                per_block = count * pool.num_planes * page  # bytes one block occupies in this chunk
+                ops = []
+                if N_out:
+                    flat_out = slot_of(a2a["out"], slot)
+                    with torch.cuda.stream(a2a["pack"]):
+                        if c >= 2:
+                            a2a["pack"].wait_event(ev_wired[slot])       # the exchange that read this slot is done
+                        pool.gather_segments(tab_out, flat_out, begin, count)
+                        ev_packed[slot].record(a2a["pack"])
+                    a2a["wire"].wait_event(ev_packed[slot])
+                    off = 0
+                    for d, n in zip(sinks, n_out):
+                        ops.append((True, flat_out[off * per_block:(off + n) * per_block], d))
+                        off += n
+                if N_in:
+                    flat_in = slot_of(a2a["in"], slot)
                     if c >= 2:
-                        a2a["pack"].wait_event(ev_wired[slot])       # the exchange that read this slot is done
-                    pool.gather(ids_out, out=view_out, layer_begin=begin, layer_count=count)
-                    ev_packed[slot].record(a2a["pack"])
-                a2a["wire"].wait_event(ev_packed[slot])
-                off = 0
-                for d, n in zip(sinks, n_out):
-                    if whole_chunk(rank, d):                         # the pair's chunk is one contiguous run
-                        ops.append((True, flat_out, d))
-                    else:
-                        for lp in range(count * pool.num_planes):    # (layer, plane) rows of the packed buffer
-                            start = (lp * N_out + off) * page
-                            ops.append((True, flat_out[start:start + n * page], d))
-                    off += n
-            if N_in:
-                flat_in, view_in = slot_view(a2a["in"], slot, N_in, count)
-                if c >= 2:
-                    a2a["wire"].wait_event(ev_unpacked[slot])        # the scatter that read this slot is done
-                off = 0
-                for s_rank, n in zip(sources, n_in):
-                    if whole_chunk(s_rank, rank):
-                        ops.append((False, flat_in, s_rank))
-                    else:
-                        for lp in range(count * pool.num_planes):
-                            start = (lp * N_in + off) * page
-                            ops.append((False, flat_in[start:start + n * page], s_rank))
-                    off += n
-            with torch.cuda.stream(a2a["wire"]):
-                ctx.exchange(self._nccl_comm, ops)
-                ev_wired[slot].record(a2a["wire"])
-            if N_in:
-                with torch.cuda.stream(a2a["unpack"]):
-                    a2a["unpack"].wait_event(ev_wired[slot])
-                    pool.scatter(ids_in, view_in, layer_begin=begin, layer_count=count)
-                    ev_unpacked[slot].record(a2a["unpack"])
-    for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
-        main.wait_stream(st)
-    torch.cuda.synchronize(self.device)
-    rc, _ = ctx.status()
-    dist.barrier(group=self.process_group)
-    if rc != _lib.OK:
-        return {"error": f"alltoall failed on device: {_lib.last_error()}", "bytes": 0, "blocks": 0}
-    return {"bytes": (N_out + N_in) * pool.block_bytes(), "blocks": N_out + N_in}
-
-
-V0Worker._migrate_alltoall = _migrate_alltoall
-
-
-def _lib_ids(ids):
-    from ...kv_pool import _as_host_ids
-    return _as_host_ids(ids)
+                        a2a["wire"].wait_event(ev_unpacked[slot])        # the scatter that read this slot is done
+                    off = 0
+                    for s_rank, n in zip(sources, n_in):
+                        ops.append((False, flat_in[off * per_block:(off + n) * per_block], s_rank))
+                        off += n
+                with torch.cuda.stream(a2a["wire"]):
+                    ctx.exchange(self._nccl_comm, ops)
+                    ev_wired[slot].record(a2a["wire"])
+                if N_in:
+                    with torch.cuda.stream(a2a["unpack"]):
+                        a2a["unpack"].wait_event(ev_wired[slot])
+                        pool.scatter_segments(tab_in, flat_in, begin, count)
+                        ev_unpacked[slot].record(a2a["unpack"])
+        for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
+            main.wait_stream(st)
+        return N_out + N_in

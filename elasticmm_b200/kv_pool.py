@@ -313,9 +313,15 @@ class KVPool:
         return phys.data_ptr(), phys.numel() * phys.element_size()
 
     def upload_ids(self, ids: IdList) -> torch.Tensor:
-        """int32 device table from a host list (stream ordered, pinned staging)."""
-        host = torch.from_numpy(_as_host_ids(ids).astype(np.int32)).pin_memory()
-        return host.to(self.device, non_blocking=True)
+        """int32 device table from a host list: staged through the library's pinned ring and
+        copied on the current stream, with no pinned allocation and no synchronisation per call."""
+        host = _as_host_ids(ids)
+        n = host.shape[0]
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        if n:
+            _lib.check(self.ctx._lib.emm_upload_ids(self.ctx._h, host.ctypes.data, n, dev.data_ptr(),
+                                                    _stream_ptr(self.device)))
+        return dev
 
     @staticmethod
     def _check_table(t: torch.Tensor, device: torch.device) -> None:
@@ -379,8 +385,7 @@ class KVPool:
         self._validated(flat, unique=unique)
         prefix = np.zeros(len(counts) + 1, dtype=np.int64)
         np.cumsum(counts, out=prefix[1:])
-        both = torch.from_numpy(np.concatenate([flat, prefix]).astype(np.int32)).pin_memory()
-        dev = both.to(self.device, non_blocking=True)
+        dev = self.upload_ids(np.concatenate([flat, prefix]))  # one staged copy for the table and its prefix sums
         return counts, int(prefix[-1]), dev[: flat.shape[0]], dev[flat.shape[0]:]
 
     def gather_many(self, id_lists: Sequence[IdList]) -> List[torch.Tensor]:
@@ -424,6 +429,30 @@ class KVPool:
             _lib.check(self.ctx._lib.emm_scatter_many(
                 self._h, C.c_void_p(ids.data_ptr()), C.c_void_p(prefix.data_ptr()), len(counts), total,
                 C.c_void_p(flat.data_ptr()), nbytes, C.c_void_p(_stream_ptr(self.device))))
+
+    def gather_segments(self, tables, flat: torch.Tensor, layer_begin: int, layer_count: int) -> None:
+        """Packs `layer_count` layers of several segments' blocks into `flat`, one contiguous
+        [layer_count, planes, n_r, page] run per segment (tables from many_tables): the packed side of a
+        rebalancing exchange, where a segment is everything one peer gets of this chunk of layers."""
+        counts, total, ids, prefix = tables
+        nbytes = self.packed_bytes(total, layer_count)
+        if flat.numel() * flat.element_size() < nbytes or not flat.is_contiguous():
+            raise ValueError("flat buffer too small or not contiguous")
+        if total:
+            _lib.check(self.ctx._lib.emm_gather_many_layers(
+                self._h, layer_begin, layer_count, ids.data_ptr(), prefix.data_ptr(), len(counts), total,
+                flat.data_ptr(), nbytes, _stream_ptr(self.device)))
+
+    def scatter_segments(self, tables, flat: torch.Tensor, layer_begin: int, layer_count: int) -> None:
+        """The inverse of gather_segments on the receiving pool."""
+        counts, total, ids, prefix = tables
+        nbytes = self.packed_bytes(total, layer_count)
+        if flat.numel() * flat.element_size() < nbytes or not flat.is_contiguous():
+            raise ValueError("flat buffer too small or not contiguous")
+        if total:
+            _lib.check(self.ctx._lib.emm_scatter_many_layers(
+                self._h, layer_begin, layer_count, ids.data_ptr(), prefix.data_ptr(), len(counts), total,
+                flat.data_ptr(), nbytes, _stream_ptr(self.device)))
 
     def _split_many(self, flat: torch.Tensor, counts: Sequence[int]) -> List[torch.Tensor]:
         out, pos = [], 0
@@ -564,28 +593,34 @@ class KVPool:
 
         `key` / `value` are [L, T, H, D] buffers and `slot_mapping` a [T] int64
         buffer that the caller refills in place every step (the usual shape of
-        a graph-captured decode step). Returns `append(layer)`, which launches
-        reshape_and_cache for that layer on the current stream at the cost of
-        one foreign call.
+        a graph-captured decode step). Returns `append(layer, stream=None)`,
+        which launches reshape_and_cache for that layer at the cost of one
+        three-argument foreign call (emm_append_bound). `stream` is a raw
+        cudaStream_t handle (`torch.cuda.current_stream().cuda_stream`); a
+        runner that issues all layers of a step on one stream looks it up once
+        per step and passes it in, otherwise the current stream is looked up
+        on every call.
         """
         T = self._check_kv(key, value, slot_mapping, 1)
         if key.shape[0] != self.num_layers:
             raise ValueError(f"key has {key.shape[0]} layers, pool has {self.num_layers}")
         e = self.elem_size
-        fn, h = self._emm_append, self._h
-        kp, vp, sp = key.data_ptr(), value.data_ptr(), slot_mapping.data_ptr()
-        kls, vls = key.stride(0) * e, value.stride(0) * e
-        kts, vts = key.stride(1) * e, value.stride(1) * e
+        lib = self.ctx._lib
+        handle = C.c_void_p()
+        _lib.check(lib.emm_append_bind(self._h, key.data_ptr(), value.data_ptr(), key.stride(0) * e, key.stride(1) * e,
+                                       value.stride(0) * e, value.stride(1) * e, slot_mapping.data_ptr(), T,
+                                       C.byref(handle)))
+        fn, h = lib.emm_append_bound, handle.value
         device = self.ctx.device
-        keep = (key, value, slot_mapping)  # the closure keeps the buffers alive
+        current_stream = torch.cuda.current_stream
 
-        def append(layer: int) -> None:
-            rc = fn(h, layer, kp + layer * kls, vp + layer * vls, kts, vts, sp, T,
-                    torch.cuda.current_stream(device).cuda_stream)
+        def append(layer: int, stream: Optional[int] = None) -> None:
+            rc = fn(h, layer, current_stream(device).cuda_stream if stream is None else stream)
             if rc:
                 _lib.check(rc)
 
-        append.buffers = keep
+        append.buffers = (key, value, slot_mapping, self)  # the closure keeps the buffers and the pool alive
+        append.release = lambda: lib.emm_append_unbind(h)
         return append
 
     def append_all_layers(self, key: torch.Tensor, value: torch.Tensor,

@@ -44,6 +44,7 @@ extern "C" {
 
 typedef struct emm_ctx emm_ctx;   /* one per process and device; not thread safe */
 typedef struct emm_pool emm_pool; /* geometry + per-layer base pointers of one pool */
+typedef struct emm_append_binding emm_append_binding; /* a validated per-layer append over static buffers */
 
 enum emm_status {
   EMM_OK = 0,
@@ -91,7 +92,10 @@ enum emm_option {
   EMM_OPT_LDG_UNROLL = 5,    /* 16-byte loads in flight per thread, LDG variant (1,2,4,8) */
   EMM_OPT_MAX_CTAS = 6,      /* cap on the grid (0 = none) */
   EMM_OPT_REMOTE_VARIANT = 7, /* family used when a side is a peer GPU's or pinned host memory (default LDG) */
-  EMM_OPT_L2_HINT = 8         /* bulk variant: bit 0 loads, bit 1 stores carry an L2 evict-first hint (default 0) */
+  EMM_OPT_L2_HINT = 8,        /* bulk variant: bit 0 loads, bit 1 stores carry an L2 evict-first hint (default 0) */
+  EMM_OPT_WAIT_LIMIT_NS = 9   /* bulk variant: longest one device-side wait for a load may last, in ns
+                                 (default 2 s, range 1 us .. 60 s); when it runs out the kernel records
+                                 EMM_ERR_TIMEOUT in the status word, drains and returns */
 };
 
 /* ---- library ---------------------------------------------------------- */
@@ -194,6 +198,21 @@ int emm_gather_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_
 int emm_scatter_many(emm_pool *pool, const int32_t *d_ids, const uint32_t *d_seg_prefix, int32_t num_segs,
                      int32_t n_total, const void *d_packed, uint64_t packed_bytes, void *stream);
 
+/* The same on a layer range: segment r holds [layer_count, planes, n_r, page]
+ * and starts layer_count*planes*page*seg_prefix[r] bytes into `d_packed`
+ * (`packed_bytes` = layer_count*planes*n_total*page). With one segment per
+ * peer this is the packed side of a rebalancing exchange: a source packs a
+ * chunk of layers as [sink][layer][plane][n_sink][page], so that each sink's
+ * share is ONE contiguous message, and a sink unpacks [source][layer][plane]
+ * [n_source][page] the same way. The reference sends one message per layer
+ * (elasticmm/engine/v0/worker.py:676-682). */
+int emm_gather_many_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const int32_t *d_ids,
+                           const uint32_t *d_seg_prefix, int32_t num_segs, int32_t n_total, void *d_packed,
+                           uint64_t packed_bytes, void *stream);
+int emm_scatter_many_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_count, const int32_t *d_ids,
+                            const uint32_t *d_seg_prefix, int32_t num_segs, int32_t n_total,
+                            const void *d_packed, uint64_t packed_bytes, void *stream);
+
 /* Block copy: dst[l][p][dst_ids[i]] = src[l][p][src_ids[i]] with no staging
  * buffer. src and dst may be the same pool (compaction; id sets must not
  * overlap), two pools on one GPU, a pool in pinned host memory (swap), or a
@@ -216,6 +235,15 @@ int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d
 int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
                       const int64_t *h_dst_ids, int32_t n, void *stream);
 
+/* Uploads a HOST int64 list as int32 into caller-owned device memory `d_out`
+ * (n entries) through the context's pinned staging ring, stream ordered, with
+ * no allocation in steady state and no device synchronisation. For tables a
+ * caller keeps on the device across calls (the device-table entries above and
+ * the seg_prefix arrays); values must lie in [0, 2^31). The reference uploads
+ * its id lists with a synchronous torch.tensor(..., device=...)
+ * (elasticmm/engine/v0/worker.py:597,628). */
+int emm_upload_ids(emm_ctx *ctx, const int64_t *h_values, int32_t n, int32_t *d_out, void *stream);
+
 /* Gather for callers that must not allocate device memory. No counterpart in
  * the reference. Some hosts cannot afford a cudaMalloc on this path: a serving
  * process that has already handed nearly all HBM to its own caching allocator
@@ -233,12 +261,31 @@ int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
  * any stream capture begins. All calls share the one array: two calls whose
  * kernels may overlap on the GPU (different streams, no ordering) race on it;
  * calls on one stream are safe. Nothing in this call invokes cudaMalloc,
- * cudaFree or any allocating library routine. */
+ * cudaFree or any allocating library routine. The table and the layer
+ * addresses are uploaded from ordinary (pageable) host memory, so the call
+ * waits on the host until earlier work on `stream` has finished before it
+ * returns; what it saves is the allocation, not that wait. A stream that is
+ * being captured is refused with EMM_ERR_BAD_ARG, because the upload happens at
+ * call time. Ids are checked on the host, so the kernel has no bad id to
+ * report; a device-side wait that runs out is not reported through this entry
+ * (it has no context whose status word could be read). */
 #define EMM_NOALLOC_MAX_IDS 16384
 #define EMM_NOALLOC_MAX_LAYERS 256
 int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const *h_layer_ptrs,
                        const int64_t *h_ids, int32_t n, void *d_packed, uint64_t packed_bytes,
                        void *stream);
+
+/* Test hook, not for production use: emm_gather with `extra_tx_bytes` added to
+ * the byte count every load is expected to deliver, so that no device-side
+ * wait of the bulk-copy kernel can complete. Each lane gives up after the
+ * context's EMM_OPT_WAIT_LIMIT_NS, records EMM_ERR_TIMEOUT in the status word
+ * and returns; every load it issued has long landed by then, so nothing is in
+ * flight when the kernel ends, the packed buffer is left partly written and
+ * the context stays usable. It lets a test run the time-out path without a
+ * fault, a trap or an unbounded wait. No counterpart in the reference (its
+ * time-out is the host-side poll at elasticmm/engine/v0/worker.py:806-812). */
+int emm_test_gather_expect_overcount(emm_pool *pool, const int32_t *d_ids, int32_t n, void *d_packed,
+                                     uint64_t packed_bytes, uint32_t extra_tx_bytes, void *stream);
 
 /* ---- per-token append -------------------------------------------------- */
 
@@ -261,6 +308,22 @@ int emm_append_all_layers(emm_pool *pool, const void *d_key, const void *d_value
                           int64_t key_layer_stride, int64_t key_token_stride,
                           int64_t value_layer_stride, int64_t value_token_stride,
                           const int64_t *d_slot_mapping, int32_t num_tokens, void *stream);
+
+/* The per-layer call for a decode loop that refills the SAME key / value /
+ * slot-mapping buffers every step (the shape of a graph-captured or
+ * static-buffer model runner): emm_append_bind validates the buffers once
+ * ([L, T, H, D] key and value with the given strides in bytes, one [T] int64
+ * slot mapping) and emm_append_bound(binding, layer, stream) then costs one
+ * short foreign call plus the launch. Same kernel and same result as
+ * emm_append(pool, layer, key + layer*key_layer_stride, ...). The binding
+ * keeps pointers only: the buffers and the pool must outlive it. The
+ * reference reaches vLLM's op once per layer in the same way
+ * (elasticmm/engine/v0/worker_steps.py:281,438). */
+int emm_append_bind(emm_pool *pool, const void *d_key, const void *d_value, int64_t key_layer_stride,
+                    int64_t key_token_stride, int64_t value_layer_stride, int64_t value_token_stride,
+                    const int64_t *d_slot_mapping, int32_t num_tokens, emm_append_binding **out);
+int emm_append_bound(emm_append_binding *binding, int32_t layer, void *stream);
+int emm_append_unbind(emm_append_binding *binding);
 
 /* ---- compaction planning (host only) ---------------------------------- */
 

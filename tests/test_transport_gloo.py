@@ -174,3 +174,98 @@ def test_receive_from_a_silent_peer_times_out_on_the_host():
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(_absent_peer_worker, args=(2, _free_port(), d), nprocs=2, join=True)
         assert torch.load(os.path.join(d, "r1.pt"))["err"] is not None
+
+
+class _StubPool:
+    """Stands in for KVPool on a CPU rank: only the host-side id checks are needed."""
+
+    def __init__(self, num_blocks):
+        self.num_blocks = num_blocks
+
+    def _validated(self, host, unique=False):
+        import numpy as np
+
+        from elasticmm_b200 import _lib
+
+        host = np.asarray(host)
+        if host.size and (host.min() < 0 or host.max() >= self.num_blocks):
+            raise _lib.EmmError(_lib.ERR_ID_RANGE, f"block id outside [0, {self.num_blocks})")
+        if unique and np.unique(host).size != host.size:
+            raise _lib.EmmError(_lib.ERR_DUPLICATE, "duplicate destination block id")
+        return host
+
+    def block_bytes(self):
+        return 1024
+
+
+def _host_worker(rank, mapped_peers, pushes):
+    """A V0Worker without a GPU: the constructor is bypassed, device waits are no-ops and the push
+    'kernel' records what it was asked to move. Everything else of migrate() is the product code."""
+    from elasticmm_b200.engine.v0.worker import V0Worker
+
+    class HostOnlyWorker(V0Worker):
+        def _own_stream_sync(self):
+            pass
+
+        def _device_error(self, what):
+            return None
+
+        def p2p_push_kv(self, dst_rank, src_blocks, dst_blocks):
+            pushes.append((dst_rank, len(src_blocks)))
+            return {"bytes": len(src_blocks) * 1024, "blocks": len(src_blocks)}
+
+    w = object.__new__(HostOnlyWorker)
+    w.device = torch.device("cpu")
+    w.process_group = None
+    w.global_rank = rank
+    w.pool = _StubPool(GEOM["NB"])
+    w.peer_pools = {p: _StubPool(GEOM["NB"]) for p in mapped_peers}
+    w._nccl_comm = None
+    return w
+
+
+def _agreement_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    plan = MigrationPlan([Transfer("a", 0, 2, (1, 2, 3), (4, 5, 6)), Transfer("b", 1, 2, (7,), (9,)),
+                          Transfer("c", 1, 3, (8, 9), (0, 1))])
+    results = {}
+    # 1. rank 1 has not mapped the pool of rank 3: every rank must return an error, and nothing is pushed
+    pushes = []
+    mapped = {0: [2], 1: [2], 2: [], 3: []}[rank]
+    results["unmapped"] = (_host_worker(rank, mapped, pushes).migrate(plan, method="push"), list(pushes))
+    # 2. a destination block used twice on rank 2 (seen by rank 2 only)
+    bad = MigrationPlan([Transfer("a", 0, 2, (1, 2), (4, 5)), Transfer("b", 1, 2, (7,), (5,))])
+    pushes = []
+    results["duplicate"] = (_host_worker(rank, {0: [2], 1: [2, 3], 2: [], 3: []}[rank], pushes).migrate(bad, "push"),
+                            list(pushes))
+    # 3. all-to-all without a communicator fails on every rank before any exchange
+    results["no_comm"] = (_host_worker(rank, [], []).migrate(plan, method="alltoall"), [])
+    # 4. the good case
+    pushes = []
+    results["ok"] = (_host_worker(rank, {0: [2], 1: [2, 3], 2: [], 3: []}[rank], pushes).migrate(plan, "push"),
+                     list(pushes))
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_every_rank_returns_the_error_when_one_rank_fails_a_host_check():
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_agreement_worker, args=(4, _free_port(), d), nprocs=4, join=True)
+        res = [torch.load(os.path.join(d, f"r{r}.pt")) for r in range(4)]
+    for r in range(4):
+        for case in ("unmapped", "duplicate", "no_comm"):
+            out, pushes = res[r][case]
+            assert "error" in out and out["bytes"] == 0 and pushes == [], (r, case, out)
+    assert "not mapped" in res[1]["unmapped"][0]["error"]
+    assert "another rank" in res[0]["unmapped"][0]["error"]
+    assert "duplicate" in res[2]["duplicate"][0]["error"]
+    assert all("init_native_nccl" in res[r]["no_comm"][0]["error"] for r in range(4))
+    assert res[0]["ok"] == ({"bytes": 3 * 1024, "blocks": 3}, [(2, 3)])
+    assert res[1]["ok"] == ({"bytes": 3 * 1024, "blocks": 3}, [(2, 1), (3, 2)]) or \
+        res[1]["ok"] == ({"bytes": 3 * 1024, "blocks": 3}, [(3, 2), (2, 1)])
+    assert res[2]["ok"][0] == {"bytes": 0, "blocks": 0} and res[3]["ok"][0] == {"bytes": 0, "blocks": 0}

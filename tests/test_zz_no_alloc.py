@@ -51,6 +51,48 @@ def test_two_calls_in_a_row_match_the_allocating_entry(geom):
     assert ctx.status()[0] == _lib.OK
 
 
+def test_a_warm_call_allocates_nothing_and_the_largest_table_fits():
+    """Free device memory is the same before and after a warm call (the caller owns the
+    output), also at the largest table the fixed array holds."""
+    ctx = get_context(0)
+    cpu = kv_oracle.make_pool(2, 8, 4, 2, 8, torch.float16, 2)             # 128-byte pages
+    pool = KVPool([t.cuda() for t in cpu], ctx)
+    n = _lib.NOALLOC_MAX_IDS
+    ids = (torch.arange(n) * 5 % 8).tolist()                                # repeats are fine for a gather
+    out = pool.new_packed(n)
+    assert _noalloc_gather(pool, ids[:7], out[:, :, :7].contiguous()) == _lib.OK   # first call on the device: set-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    assert _noalloc_gather(pool, ids, out) == _lib.OK, _lib.last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before
+    want = kv_oracle.extract_kv_blocks(cpu, ids)
+    assert kv_oracle.bit_equal(out.cpu(), want)
+
+
+def test_a_capturing_stream_is_refused():
+    """The table is uploaded from host memory at call time, so the entry refuses a stream under capture."""
+    ctx = get_context(0)
+    cpu = kv_oracle.make_pool(2, 8, 4, 2, 8, torch.float16, 3)
+    pool = KVPool([t.cuda() for t in cpu], ctx)
+    out = pool.new_packed(2)
+    assert _noalloc_gather(pool, [1, 2], out) == _lib.OK                    # set-up outside any capture
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            rc = _noalloc_gather(pool, [1, 2], out)
+            out.add_(0)                                                     # keep the captured graph non-empty
+    assert rc == _lib.ERR_BAD_ARG
+    assert b"capturing" in _lib.load().emm_last_error()
+    torch.cuda.synchronize()
+    assert _noalloc_gather(pool, [3, 4], out) == _lib.OK
+    torch.cuda.synchronize()
+    assert kv_oracle.bit_equal(out.cpu(), kv_oracle.extract_kv_blocks(cpu, [3, 4]))
+
+
 def test_a_small_ring_here_leaves_the_larger_launches_of_a_context_working():
     """Both entry points launch the same kernel, whose shared-memory limit is
     per device: a 16 KiB-page call here (96 KiB ring) between two 128 KiB-ring
