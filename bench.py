@@ -10,7 +10,9 @@ One "step" migrates every request of the workload once.
   N = 2   Qwen2.5-VL-7B-shaped pool (28 layers, 4 KV heads, bf16), 128 requests with a 576-token image
           prefix: rank 0 -> rank 1 (the sink pulls).
   N = 4   LLaVA-13B-shaped pool (40 layers, 40 KV heads, fp16), 512 requests: 2 sources -> 2 sinks.
-  N = 8   the same 512 requests: 2 sources -> 6 sinks, in waves bounded by the pools.
+  N = 8   the same 512 requests: 2 sources -> 6 sinks. The KV of all requests exceeds the pools, so it
+          moves in waves of half a pool; waves are not separated by a barrier (a completion ledger lets a
+          sink start the next wave of a source as soon as the wave before the last is done everywhere).
 For N > 1 launch under torchrun (one rank per GPU). The line's `value` is the
 whole-job payload rate with tables resident on the device; `e2e` is the same
 workload through the engine/v0 worker API with host block-id lists, table upload
@@ -21,6 +23,12 @@ extra objects at N = 1.
 All data is synthetic: seeded N(0,1) values with the named shapes; no model
 weights or datasets are involved. `--impl reference` times the CPU restatement
 of the reference's torch index/copy path (oracle/) on the host cores.
+
+Every line carries `verified_bit_exact`: before anything is timed, every request of every
+wave is moved once and compared bit for bit on the device with the reference's own
+indexing expression (`dst_layer[:, dst_ids]` against `src_layer[:, src_ids]`,
+elasticmm/engine/v0/worker.py:604,633); for N > 1 the expected bytes travel from the
+source to the sink through torch.distributed, independently of the kernels under test.
 """
 from __future__ import annotations
 
@@ -89,6 +97,34 @@ def make_waves(counts, capacity):
     return waves
 
 
+def build_requests(w, seed=1):
+    """(counts, waves, reqs): seeded request sizes, the waves that fit the pool, and per request (in wave
+    order) the source and destination block tables, slices of one seeded permutation per wave and side.
+    Shared by the GPU arm and the CPU reference arm so that both move the same tables."""
+    counts = request_blocks(w, seed)
+    waves = make_waves(counts, w["NB"])
+    g = torch.Generator().manual_seed(seed)
+    reqs = []
+    for wave in waves:
+        sperm, dperm = torch.randperm(w["NB"], generator=g).tolist(), torch.randperm(w["NB"], generator=g).tolist()
+        pos = 0
+        for i in wave:
+            reqs.append((sperm[pos:pos + counts[i]], dperm[pos:pos + counts[i]]))
+            pos += counts[i]
+    return counts, waves, reqs
+
+
+def mem_available_gib():
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) / (1 << 20)
+    except OSError:
+        pass
+    return 0.0
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -96,9 +132,6 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
-
-
-NVLINK_PEER_COPY_GBS = 770.0  # measured peer copy per direction per GPU on this pool
 
 
 class ClockSampler:
@@ -216,11 +249,14 @@ def cpu_model():
 
 
 class CpuPath:
-    """gather -> scatter of a workload's geometry on host tensors with the oracle port of the
-    reference's torch index/copy path, all torch threads. Bounded: a reduced pool (about 3 GiB)
-    and as many requests as fit a time budget."""
+    """gather -> scatter of a workload on host tensors with the oracle port of the reference's torch
+    index/copy path (extract_kv_blocks then write_kv_blocks), all torch threads.
 
-    def __init__(self, wname):
+    When the host has the memory, the pools have the workload's full block count and the requests use the
+    same seeded tables as the GPU arm; otherwise the pool is cut to `nb` blocks (stated in the result) and the
+    requests keep their sizes with tables drawn inside the smaller pool."""
+
+    def __init__(self, wname, full=True):
         from oracle import kv_oracle
 
         self.oracle = kv_oracle
@@ -228,42 +264,59 @@ class CpuPath:
         # torchrun pins OMP_NUM_THREADS to 1 per rank; the CPU legs run on one rank only and may use every core
         torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
         w = self.w = WORKLOADS[wname]
-        self.nb = nb = min(w["NB"], max(64, int(3 * GIB // block_bytes(w))))
+        pool_gib = w["NB"] * block_bytes(w) / GIB
+        need_gib = 2 * pool_gib + 3 * max(request_blocks(w, 1)) * block_bytes(w) / GIB + 8
+        self.full = bool(full and mem_available_gib() >= need_gib)
+        self.nb = nb = w["NB"] if self.full else min(w["NB"], max(64, int(3 * GIB // block_bytes(w))))
         dt = DT[w["dtype"]]
         shape = (2, nb, w["BS"], w["H"], w["D"])
         tile = torch.randn(1 << 16).to(dt)
         self.src, self.dst = [], []
         for _ in range(w["L"]):
-            t = torch.zeros(shape, dtype=dt)
+            t = torch.empty(shape, dtype=dt)
             flat = t.view(-1)
             whole = flat.numel() // tile.numel() * tile.numel()
             flat[:whole].view(-1, tile.numel())[:] = tile
+            flat[whole:] = 0
             self.src.append(t)
             self.dst.append(torch.zeros(shape, dtype=dt))
-        self.counts = [min(c, nb // 2) for c in request_blocks(w, 1)]
-        self.gen = torch.Generator().manual_seed(1)
+        if self.full:
+            self.counts, _, self.reqs = build_requests(w, 1)
+            self.reqs = list(self.reqs)
+        else:
+            counts = [min(c, nb // 2) for c in request_blocks(w, 1)]
+            gen = torch.Generator().manual_seed(1)
+            self.reqs = [(torch.randperm(nb, generator=gen)[:c].tolist(), torch.randperm(nb, generator=gen)[:c].tolist())
+                         for c in counts]
         self.threads = torch.get_num_threads()
         # warm-up on one small request
         kv_oracle.write_kv_blocks(self.dst, [0, 1], kv_oracle.extract_kv_blocks(self.src, [2, 3]))
 
-    def run(self, budget_s):
-        w, nb = self.w, self.nb
+    def describe(self, reqs, moved):
+        w = self.w
+        pool = (f"the full {self.nb}-block host pools, seeded permutation tables"
+                + (" (the GPU arm's)" if self.wname == "llama7b_cfg1" else "") if self.full
+                else f"host pools cut to {self.nb} blocks (of {w['NB']}; host memory), request sizes kept")
+        return (f"{reqs} of {len(self.reqs)} requests ({moved} blocks, {moved * block_bytes(w) / GIB:.1f} GiB payload) of "
+                f"{self.wname} on {pool}; extract_kv_blocks then write_kv_blocks restated with torch CPU indexing; "
+                f"{self.threads} torch threads, {os.cpu_count()} host cpus")
+
+    def run(self, budget_s=None, max_requests=None):
+        """One pass over the requests (all of them, or the first `max_requests`, or as many as fit `budget_s`)."""
+        w = self.w
         moved, reqs, t_total = 0, 0, 0.0
-        for c in self.counts:
-            s = torch.randperm(nb, generator=self.gen)[:c].tolist()
-            d = torch.randperm(nb, generator=self.gen)[:c].tolist()
+        for s, d in self.reqs[: max_requests or len(self.reqs)]:
             t0 = time.perf_counter()
             self.oracle.write_kv_blocks(self.dst, d, self.oracle.extract_kv_blocks(self.src, s))
             t_total += time.perf_counter() - t0
-            moved += c
+            moved += len(s)
             reqs += 1
-            if t_total > budget_s:
+            if budget_s is not None and t_total > budget_s:
                 break
         gbs = moved * block_bytes(w) / t_total / 1e9
         return {"value": round(gbs, 3), "unit": "GB/s", "cores": self.threads, "kind": "port",
-                "sample": f"{reqs} requests ({moved} blocks, {moved * block_bytes(w) / GIB:.1f} GiB payload) of "
-                          f"{self.wname} geometry on a {nb}-block host pool; extract_kv_blocks then write_kv_blocks "
-                          f"restated with torch CPU indexing; {self.threads} torch threads, {os.cpu_count()} host cpus",
+                "sample": self.describe(reqs, moved), "requests": reqs, "blocks": moved,
+                "nb_reduced_to": None if self.full else self.nb,
                 "seconds": round(t_total, 2), "blocks_per_s": round(moved / t_total, 1), "cpu_model": cpu_model()}
 
     def run_c(self, budget_s):
@@ -271,16 +324,13 @@ class CpuPath:
         from oracle import kv_oracle_c
 
         threads = os.cpu_count() or 1
-        w, nb = self.w, self.nb
-        gen = torch.Generator().manual_seed(1)
+        w = self.w
         moved, t_total = 0, 0.0
-        for c in self.counts:
-            s = torch.randperm(nb, generator=gen)[:c].tolist()
-            d = torch.randperm(nb, generator=gen)[:c].tolist()
+        for s, d in self.reqs:
             t0 = time.perf_counter()
             kv_oracle_c.scatter(self.dst, d, kv_oracle_c.gather(self.src, s, threads=threads), threads=threads)
             t_total += time.perf_counter() - t0
-            moved += c
+            moved += len(s)
             if t_total > budget_s:
                 break
         return {"value": round(moved * block_bytes(w) / t_total / 1e9, 3), "unit": "GB/s", "cores": threads,
@@ -289,7 +339,8 @@ class CpuPath:
 
 
 def cpu_baseline(wname, budget_s=12.0):
-    path = CpuPath(wname)
+    """The bounded CPU leg printed beside the GPU line (about 20 s of CPU work on a 3 GiB pool)."""
+    path = CpuPath(wname, full=False)
     out = path.run(budget_s)
     threads = torch.get_num_threads()
     try:  # the same path on one thread (a few seconds)
@@ -307,29 +358,48 @@ def cpu_baseline(wname, budget_s=12.0):
     return out
 
 
+REFERENCE_ARM_BUDGET_S = 240.0  # CPU seconds the whole --impl reference run may take (steps + warm-up)
+
+
 def reference_arm(args):
+    """The reference's own torch index/copy path on the host cores, on the GPU arm's workload: at N = 1
+    BASELINE config 1 as worded (2048-block pools, 64 requests, the same seeded tables) whenever the host
+    has the memory and a full step fits the time budget; otherwise a bounded sample, named in `config`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wname = {1: "llama7b_cfg1", 2: "qwen25vl7b_cfg3"}.get(args.gpus, "llava13b_cfg4")
-    per_step = max(2.0, min(10.0, 120.0 / max(1, args.steps + args.warmup)))
-    path = CpuPath(wname)
-    vals = []
-    base = None
+    w = WORKLOADS[wname]
+    path = CpuPath(wname, full=True)
+    n_runs = max(1, args.steps + args.warmup)
+    probe = path.run(max_requests=2)  # sizes the step: seconds per block on this host
+    total_blocks = sum(len(s) for s, _ in path.reqs)
+    est_full = probe["seconds"] / max(1, probe["blocks"]) * total_blocks
+    if est_full * n_runs <= REFERENCE_ARM_BUDGET_S:
+        per_step = dict(max_requests=None)
+    else:
+        per_step = dict(budget_s=max(2.0, REFERENCE_ARM_BUDGET_S / n_runs))
+    vals, base = [], None
     for i in range(args.warmup + args.steps):
-        base = path.run(per_step)
+        base = path.run(**per_step)
         if i >= args.warmup:
             vals.append(base)
     value = sum(v["value"] for v in vals) / len(vals)
     secs = sum(v["seconds"] for v in vals) / len(vals)
     base["value"] = round(value, 3)
+    whole = base["requests"] == len(path.reqs) and path.full
     line = {
         "impl": "reference", "metric": "kv_migration_payload_GBps", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
-        "config": {"workload": wname, "note": "CPU restatement of the reference's torch index/copy path on host "
-                   "cores; the reference is pure Python+torch on this path and needs Ray and vLLM to run as shipped; "
-                   "the transport leg has no CPU counterpart"},
+        "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
+                   "requests": w["requests"], "blocks_per_step": total_blocks,
+                   "sample_requests": base["requests"], "sample_blocks": base["blocks"],
+                   "nb_reduced_to": base["nb_reduced_to"], "whole_workload_per_step": whole,
+                   "path": "gather -> packed buffer -> scatter",
+                   "note": "CPU restatement of the reference's torch index/copy path on host cores; the reference "
+                           "is pure Python+torch on this path and needs Ray and vLLM to run as shipped; the "
+                           "transport leg of a multi-GPU migration has no CPU counterpart"},
         "cpu_baseline": base,
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -352,16 +422,7 @@ def bench_single(args):
     src_worker = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 1))
     dst_worker = V0Worker(dtype=w["dtype"], device=device, kv_cache=gpu_pool(w, device, 0, guard=True))
     src, dst = src_worker.pool, dst_worker.pool
-    counts = request_blocks(w, 1)
-    waves = make_waves(counts, w["NB"])
-    g = torch.Generator().manual_seed(1)
-    reqs = []  # (src ids, dst ids) per request, in wave order
-    for wave in waves:
-        sperm, dperm = torch.randperm(w["NB"], generator=g).tolist(), torch.randperm(w["NB"], generator=g).tolist()
-        pos = 0
-        for i in wave:
-            reqs.append((sperm[pos:pos + counts[i]], dperm[pos:pos + counts[i]]))
-            pos += counts[i]
+    counts, waves, reqs = build_requests(w, 1)  # (src ids, dst ids) per request, in wave order
     total_blocks = sum(counts)
     payload = total_blocks * block_bytes(w)
     dev_tables = [(src.upload_ids(s), dst.upload_ids(d)) for s, d in reqs]
@@ -383,15 +444,26 @@ def bench_single(args):
         rc, _ = ctx.status()  # device -> host read of the status word, synchronises
         assert rc == 0
 
-    # correctness gate before timing: per-block checksums of the last wave
-    step_device()
-    rc, detail = ctx.status()
-    assert rc == 0, f"device status {rc} ({detail})"
-    s_sum, d_sum = block_checksums(src.layers), block_checksums(dst.layers)
-    last = waves[-1]
-    s_last = torch.tensor([b for i in range(len(reqs) - len(last), len(reqs)) for b in reqs[i][0]], device=device)
-    d_last = torch.tensor([b for i in range(len(reqs) - len(last), len(reqs)) for b in reqs[i][1]], device=device)
-    verified = bool(torch.equal(s_sum[s_last], d_sum[d_last]))
+    # Correctness gate before timing: every request of every wave is moved once and compared bit for bit on
+    # the device with the reference's own indexing expression, dst_layer[:, dst_ids] against
+    # src_layer[:, src_ids] per layer (waves reuse destination blocks, so each wave is checked before the next).
+    verified, verified_requests, pos = True, 0, 0
+    for wave in waves:
+        for k in range(len(wave)):
+            s_dev, d_dev = dev_tables[pos + k]
+            buf = packed_for(s_dev.numel())
+            src.gather(s_dev, out=buf)
+            dst.scatter(d_dev, buf)
+        rc, detail = ctx.status()
+        assert rc == 0, f"device status {rc} ({detail})"
+        for k in range(len(wave)):
+            s_idx = torch.tensor(reqs[pos + k][0], device=device)
+            d_idx = torch.tensor(reqs[pos + k][1], device=device)
+            for ls, ld in zip(src.layers, dst.layers):
+                verified = verified and bool(torch.equal(ld[:, d_idx].view(torch.int16), ls[:, s_idx].view(torch.int16)))
+            verified_requests += 1
+        pos += len(wave)
+    assert verified, "gather -> scatter differs from the reference's indexing expression"
 
     l0 = ctx.launch_count
     with ClockSampler(0) as clocks:
@@ -454,7 +526,30 @@ def bench_single(args):
     e2e_value = payload * e2e_steps / (ms_e2e / 1e3) / 1e9
     h2d = sum(4 * (len(s) + len(d)) for s, d in reqs)
 
-    del packed, flat, dev_tables, wave_tables, many
+    # What the reference itself executes on a GPU today: torch indexing per layer, torch.stack, index_put per
+    # layer, with the synchronous upload of the id list (elasticmm/engine/v0/worker.py:597-608,628-633).
+    def step_torch_index():
+        for (s_ids, d_ids) in reqs:
+            idx = torch.tensor(s_ids, dtype=torch.long, device=device)
+            data = torch.stack([layer[:, idx] for layer in src.layers], dim=0)
+            idx = torch.tensor(d_ids, dtype=torch.long, device=device)
+            for l, layer in enumerate(dst.layers):
+                layer[:, idx] = data[l]
+
+    del packed, flat
+    torch.cuda.empty_cache()
+    ti_steps = max(2, args.steps // 10)
+    try:
+        ms_ti = timed(step_torch_index, ti_steps, 1, device)
+        torch_index = {"value": round(payload * ti_steps / (ms_ti / 1e3) / 1e9, 2), "unit": "GB/s",
+                       "ms_per_step": round(ms_ti / ti_steps, 3), "steps": ti_steps,
+                       "path": "the reference's own expression on CUDA tensors: layer[:, idx] per layer, torch.stack, "
+                               "layer[:, idx] = data per layer (torch indexing kernels, not this library)"}
+    except Exception as e:
+        torch_index = {"error": f"{type(e).__name__}: {e}"}
+    torch.cuda.empty_cache()
+
+    del dev_tables, wave_tables, many
     extras = {}
     if not args.skip_extras:
         src_worker = dst_worker = src = dst = None
@@ -478,7 +573,9 @@ def bench_single(args):
                    "l2": f"inputs larger than L2 (two {w['NB'] * block_bytes(w) / GIB:.0f} GiB pools, "
                          f"{min(counts) * block_bytes(w) >> 20}..{max(counts) * block_bytes(w) >> 20} MiB per launch)",
                    "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
-        "verified_bit_exact_checksum": verified,
+        "verified_bit_exact": verified, "verified_waves": len(waves), "verified_requests": verified_requests,
+        "verified_how": "torch.equal of dst_layer[:, dst_ids] and src_layer[:, src_ids] (int16 views) per layer, "
+                        "every request of every wave, on the device before timing",
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": round(TRAFFIC_RATIO["page_copy"] * 2 * payload / len(reqs)),
                      "peak_kind": f"of {peak_kind}", "frac_of_8tbs_nominal": round(achieved / 8000.0, 4),
@@ -490,7 +587,7 @@ def bench_single(args):
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "cpu_baseline": cpu,
-        "variants": {"direct_block_copy": {
+        "variants": {"torch_index_gpu": torch_index, "direct_block_copy": {
             "value": round(payload * direct_steps / (ms_direct / 1e3) / 1e9, 2), "unit": "GB/s",
             "hbm_gbs": round(2 * payload * direct_steps / (ms_direct / 1e3) / 1e9, 1),
             "ms_per_step": round(ms_direct / direct_steps, 3),
@@ -516,14 +613,17 @@ def bench_single(args):
     print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for page_copy_bulk, from the ncu capture
-# summarised in profiles/page_copy_bulk_llama7b_small.md (105-block launch of the --small case); traffic grows in
-# proportion to the blocks a launch moves, so the ratio is scaled to this run's mean launch.
+# DRAM bytes (read + written, ncu dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes for one
+# page_copy_bulk launch: 880.88 MB read and 832.83 MB written for 2 x 880.80 MB algorithmic, captured on a 105-block
+# launch of the --small case. Traffic grows in proportion to the blocks a launch moves, so the ratio is applied to
+# this run's mean launch.
 TRAFFIC_RATIO = {"page_copy": (880.883456 + 832.828416) / (2 * 880.80384)}
 
 
 def bench_append(ctx, device, args):
-    """Decode-time append: reshape_and_cache of [256, 8, 128] bf16 per layer into a 32-layer, 16384-block pool."""
+    """Decode-time append: reshape_and_cache of [256, 8, 128] bf16 per layer into a 32-layer, 16384-block pool.
+    Successive steps take their new-token K/V from a ring of buffers larger than L2 and fresh slot sets, so
+    that the rows are read from HBM as in a decode loop (one step's 33 MB of rows would otherwise stay in L2)."""
     from elasticmm_b200 import KVPool
 
     w = WORKLOADS["append_cfg2"]
@@ -538,23 +638,26 @@ def bench_append(ctx, device, args):
         maps.append(s.to(device))
     valid = int((maps[0] >= 0).sum())
     gd = torch.Generator(device=device).manual_seed(3)
-    key = torch.randn(L, T, H, D, generator=gd, device=device, dtype=torch.bfloat16)
-    value = torch.randn(L, T, H, D, generator=gd, device=device, dtype=torch.bfloat16)
+    ring = 8  # 8 x (16.8 MB key + 16.8 MB value) = 268 MB, more than the 126 MB L2
+    keys = [torch.randn(L, T, H, D, generator=gd, device=device, dtype=torch.bfloat16) for _ in range(ring)]
+    values = [torch.randn(L, T, H, D, generator=gd, device=device, dtype=torch.bfloat16) for _ in range(ring)]
     it = {"i": 0}
 
     def per_layer():
-        s = maps[it["i"] % 16]
+        i = it["i"]
         it["i"] += 1
+        s, key, value = maps[i % 16], keys[i % ring], values[i % ring]
         for l in range(L):
             pool.append(l, key[l], value[l], s)
 
     def all_layers():
-        s = maps[it["i"] % 16]
+        i = it["i"]
         it["i"] += 1
-        pool.append_all_layers(key, value, s)
+        pool.append_all_layers(keys[i % ring], values[i % ring], maps[i % 16])
 
     steps = max(args.steps, 50)
-    out = {"workload": "append_cfg2", "tokens_per_step": T, "valid_tokens": valid, "layers": L}
+    out = {"workload": "append_cfg2", "tokens_per_step": T, "valid_tokens": valid, "layers": L,
+           "l2": f"key/value rotate over {ring} buffer pairs ({ring * 2 * keys[0].numel() * 2 >> 20} MiB), slots over 16 sets"}
     ms = timed(all_layers, steps, 5, device)
     row = H * D * 2
     algo = valid * L * (4 * row + 8)  # K and V rows read and written, plus the slot
@@ -565,36 +668,39 @@ def bench_append(ctx, device, args):
     ms = timed(per_layer, steps, 5, device)
     out["per_layer_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
                               "launches_per_step": L}
-    slot_buf = maps[0].clone()
-    bound = pool.bind_append(key, value, slot_buf)
+    # static buffers refilled in place every step, validated once; the step's stream is looked up once per step
+    key_buf, value_buf, slot_buf = keys[0].clone(), values[0].clone(), maps[0].clone()
+    bound = pool.bind_append(key_buf, value_buf, slot_buf)
 
     def per_layer_bound():
         slot_buf.copy_(maps[it["i"] % 16])
         it["i"] += 1
+        stream = torch.cuda.current_stream(device).cuda_stream
         for l in range(L):
-            bound(l)
+            bound(l, stream)
 
     ms = timed(per_layer_bound, steps, 5, device)
     out["per_layer_bound_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)),
                                     "us_per_step": round(ms * 1e3 / steps, 2), "launches_per_step": L,
-                                    "what": "static key/value/slot buffers validated once (KVPool.bind_append)"}
+                                    "what": "static key/value/slot buffers validated once (KVPool.bind_append -> "
+                                            "emm_append_bound), one three-argument foreign call per layer"}
     # CUDA-graph replay of the per-layer sequence (how a captured decode step issues it)
     try:
         stream = torch.cuda.Stream(device)
         graph = torch.cuda.CUDAGraph()
-        s0 = maps[0]
         with torch.cuda.stream(stream):
             for l in range(L):
-                pool.append(l, key[l], value[l], s0)
+                bound(l, stream.cuda_stream)
             stream.synchronize()
             with torch.cuda.graph(graph, stream=stream):
                 for l in range(L):
-                    pool.append(l, key[l], value[l], s0)
+                    bound(l, stream.cuda_stream)
         ms = timed(graph.replay, steps, 5, device)
         out["per_layer_graph_replay"] = {"tokens_per_s": round(T * steps / (ms / 1e3)),
                                          "us_per_step": round(ms * 1e3 / steps, 2), "launches_per_step": L}
     except Exception as e:  # graph capture is a reporting extra, not part of the contract
         out["per_layer_graph_replay"] = {"error": f"{type(e).__name__}: {e}"}
+    bound.release()
     return out
 
 
@@ -672,11 +778,75 @@ def bench_compaction(ctx, device, args):
 # N > 1
 # ---------------------------------------------------------------------------
 
+NVLINK_NOMINAL_GBS = 900.0  # NVLink 5, per direction per GPU
+
+
+def build_wave_plans(w, sources, sinks, seed=4):
+    """Splits the workload's requests over the sources, assigns each a seeded sink, and packs them into waves.
+
+    A wave may occupy half of every pool (source and sink blocks of wave k are reused by wave k + 2, so two
+    waves can be in flight). Within a wave a source fills its half so that its sinks receive about the same
+    number of blocks: it repeatedly gives the sink that has the least so far the largest remaining request
+    that still fits. Block tables are seeded permutations of the half the wave may use."""
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer
+
+    counts = request_blocks(w, seed)
+    g = torch.Generator().manual_seed(seed)
+    assign = torch.randint(0, len(sinks), (len(counts),), generator=g).tolist()
+    half = w["NB"] // 2
+    remaining = {s: {d: sorted((i for i in range(len(counts)) if i % len(sources) == k and sinks[assign[i]] == d),
+                               key=lambda i: -counts[i]) for d in sinks} for k, s in enumerate(sources)}
+    plans, wv = [], 0
+    carry = {s: {d: 0.0 for d in sinks} for s in sources}  # blocks a sink is behind (+) or ahead (-) of its fair share
+    while any(lst for per in remaining.values() for lst in per.values()):
+        base = (wv % 2) * half
+        plan = MigrationPlan()
+        sink_used = {d: 0 for d in sinks}
+        sink_perm = {d: (torch.randperm(half, generator=torch.Generator().manual_seed(77 * wv + d)) + base).tolist()
+                     for d in sinks}
+        for s in sources:
+            perm = (torch.randperm(half, generator=torch.Generator().manual_seed(1000 * wv + s)) + base).tolist()
+            pos, given = 0, {d: 0 for d in sinks}
+            budget = {d: half / len(sinks) + carry[s][d] for d in sinks}
+
+            def give(d, i):
+                nonlocal pos
+                n = counts[i]
+                plan.add(Transfer(f"req{i}", s, d, tuple(perm[pos:pos + n]),
+                                  tuple(sink_perm[d][sink_used[d]:sink_used[d] + n])))
+                pos += n
+                sink_used[d] += n
+                given[d] += n
+                remaining[s][d].remove(i)
+
+            def fits(d, i):
+                return pos + counts[i] <= half and sink_used[d] + counts[i] <= half
+
+            # first every sink's fair share (plus what it is owed), the sink that is owed most first ...
+            for d in sorted(sinks, key=lambda d: -budget[d]):
+                for i in list(remaining[s][d]):
+                    if fits(d, i) and (given[d] + counts[i] <= budget[d] or given[d] == 0):
+                        give(d, i)
+            # ... then whatever still fits the source's half, largest first
+            for d, i in sorted(((d, i) for d in sinks for i in remaining[s][d]), key=lambda di: -counts[di[1]]):
+                if fits(d, i):
+                    give(d, i)
+            for d in sinks:
+                carry[s][d] = max(-half, min(half, budget[d] - given[d])) if remaining[s][d] else 0.0
+        assert plan.transfers, "a request does not fit an empty wave"
+        plans.append(plan)
+        wv += 1
+    return plans
+
+
 def bench_multi(args):
+    import hashlib
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # send/recv and peer loads only: no NVLink multicast binding
     import torch.distributed as dist
 
-    from elasticmm_b200 import _lib
-    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer, V0Worker
+    from elasticmm_b200.engine.v0 import V0Worker
+    from elasticmm_b200.engine.v0.transport import WaveLedger
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -684,6 +854,8 @@ def bench_multi(args):
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
+    store = dist.distributed_c10d._get_default_store()
+    t_start = time.monotonic()
 
     if world == 2:
         wname, sources, sinks = "qwen25vl7b_cfg3", [0], [1]
@@ -704,201 +876,230 @@ def bench_multi(args):
     if nxt not in worker.peer_pools:
         worker.attach_peer_pool(nxt, handles[nxt][0], handles[nxt][1])
 
-    # Requests are split evenly over the sources; each gets a seeded sink. A wave is bounded by the
-    # source pool (blocks live at once) and by each sink's pool; source and sink tables are seeded
-    # permutations of the pool's block ids.
-    counts = request_blocks(w, 4)
-    g = torch.Generator().manual_seed(4)
-    assign = torch.randint(0, len(sinks), (len(counts),), generator=g).tolist()
-    per_src = {s: [i for i in range(len(counts)) if i % len(sources) == k] for k, s in enumerate(sources)}
-
-    def build_plans():
-        """First-fit waves: in each wave every source takes, in order, each of its remaining requests
-        that still fits its own pool and the pool of the sink the request is assigned to (requests are
-        independent, so their order is free). Fuller waves mean fewer barriers and less imbalance."""
-        out = []
-        remaining = {s: list(per_src[s]) for s in sources}
-        wv = 0
-        while any(remaining.values()):
-            plan = MigrationPlan()
-            sink_used = {d: 0 for d in sinks}
-            sink_perm = {d: torch.randperm(w["NB"], generator=torch.Generator().manual_seed(77 * wv + d)).tolist()
-                         for d in sinks}
-            for s in sources:
-                perm = torch.randperm(w["NB"], generator=torch.Generator().manual_seed(1000 * wv + s)).tolist()
-                pos, later = 0, []
-                for i in remaining[s]:
-                    d, n = sinks[assign[i]], counts[i]
-                    if pos + n > w["NB"] or sink_used[d] + n > w["NB"]:
-                        later.append(i)
-                        continue
-                    plan.add(Transfer(f"req{i}", s, d, tuple(perm[pos:pos + n]),
-                                      tuple(sink_perm[d][sink_used[d]:sink_used[d] + n])))
-                    pos += n
-                    sink_used[d] += n
-                remaining[s] = later
-            assert plan.transfers, "a request does not fit an empty wave"
-            out.append(plan)
-            wv += 1
-        return out
-
-    plans = build_plans()
+    plans = build_wave_plans(w, sources, sinks)
     total_blocks = sum(p.total_blocks() for p in plans)
     payload = total_blocks * block_bytes(w)
+    kv = worker.kv_cache
 
-    # device-resident tables per wave, in the order this rank serves its peers: sinks hold
-    # (source, src ids, dst ids) for the pull path, sources hold (sink, ...) for the push variant
-    push_tables, pull_tables = [], []
-    for plan in plans:
-        pull = [(s,) + tuple(worker.pool.upload_ids(t) for t in plan.tables(s, rank)) for s in plan.pull_order(rank)]
-        push = [(d,) + tuple(worker.pool.upload_ids(t) for t in plan.tables(rank, d)) for d in plan.push_order(rank)]
-        pull_tables.append(pull)
-        push_tables.append(push)
+    # device-resident tables per wave: a sink holds (src ids, dst ids) per source, a source per sink (push variant)
+    pull_tables = [{s: tuple(worker.pool.upload_ids(t) for t in plan.tables(s, rank)) for s in plan.incoming(rank)}
+                   for plan in plans]
+    push_tables = [[(d,) + tuple(worker.pool.upload_ids(t) for t in plan.tables(rank, d)) for d in plan.push_order(rank)]
+                   for plan in plans]
+    epoch = {"n": 0}
+
+    def ledger(tag):
+        epoch["n"] += 1
+        return WaveLedger(store, f"bench/{tag}/{epoch['n']}")
 
     def barrier():
         dist.barrier()
-
-    streams = {p: torch.cuda.Stream(device) for p in range(world)}
-    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
-
-    def run_waves(tables, pull):
-        main = torch.cuda.current_stream(device)
-        for per in tables:
-            if pull:
-                # all sources of this sink at once, grids capped to one CTA per SM in total (measured:
-                # uncapped side-by-side pulls halve the NVSwitch rate, capped ones run at link speed)
-                cap = max(24, sm_count // max(1, len(per))) if len(per) > 1 else None
-                for peer, si, di in per:
-                    streams[peer].wait_stream(main)
-                    with torch.cuda.stream(streams[peer]):
-                        worker.peer_pools[peer].copy_blocks(worker.pool, si, di, max_ctas=cap)
-                for peer, _, _ in per:
-                    main.wait_stream(streams[peer])
-            else:
-                for peer, si, di in per:  # one sink at a time, sources start at different sinks
-                    worker.pool.copy_blocks(worker.peer_pools[peer], si, di)
-            torch.cuda.synchronize(device)
-            dist.barrier()  # wave boundary: blocks are reused only after every copy of the wave landed
-
-    def step_pull():
-        run_waves(pull_tables, True)
-
-    def step_push():
-        run_waves(push_tables, False)
-
-    def step_nccl():
-        for plan in plans:
-            res = worker.migrate(plan, method="nccl")
-            assert "error" not in res, res
-            dist.barrier()
-
-    # correctness gate: checksums of what landed against what was sent (last wave)
-    step_pull()
-    sums = block_checksums(worker.pool.layers).cpu()
-    all_sums = [None] * world
-    dist.all_gather_object(all_sums, sums)
-    verified = True
-    for t in plans[-1].transfers:
-        if t.dst_rank == rank:
-            a = all_sums[t.src_rank][list(t.src_blocks)]
-            b = sums[list(t.dst_blocks)]
-            verified = verified and bool(torch.equal(a, b))
-    flags = [None] * world
-    dist.all_gather_object(flags, verified)
-    verified = all(flags)
 
     def max_ms(ms):
         t = torch.tensor([ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def all_true(flag):
+        t = torch.tensor([1 if flag else 0], device=device, dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    wave_times = []
+
+    def step_pull():
+        res = worker.migrate_waves(plans, ledger("pull"), depth=2, tables=pull_tables)
+        assert "error" not in res, res
+        wave_times.append(res["wave_ms"])
+
+    def step_e2e():
+        res = worker.migrate_waves(plans, ledger("e2e"), depth=2)
+        assert "error" not in res, res
+
+    def step_method(method):
+        def run():
+            for plan in plans:
+                res = worker.migrate(plan, method=method)
+                assert "error" not in res, res
+        return run
+
+    def step_push_resident():
+        for per in push_tables:
+            for peer, si, di in per:  # one sink at a time, sources start at different sinks
+                worker.pool.copy_blocks(worker.peer_pools[peer], si, di)
+            torch.cuda.synchronize(device)
+            dist.barrier()  # blocks of a wave are reused only after every copy of the wave has landed
+
+    # ---- correctness gates (nothing here is timed) --------------------------------------------------------
+    def verify_wave(plan):
+        """Full bit compare of one wave: for every transfer, in the plan's order on every rank, the source
+        evaluates the reference's expression on its own pool (stack of layer[:, src_ids]) and ships it with
+        torch.distributed; the sink evaluates the same expression on what landed (layer[:, dst_ids]) and
+        compares with torch.equal."""
+        ok = True
+        for t in plan.transfers:
+            if t.src_rank == rank:
+                idx = torch.tensor(t.src_blocks, dtype=torch.long, device=device)
+                dist.send(torch.stack([layer[:, idx] for layer in kv], dim=0), dst=t.dst_rank)
+            elif t.dst_rank == rank:
+                idx = torch.tensor(t.dst_blocks, dtype=torch.long, device=device)
+                got = torch.stack([layer[:, idx] for layer in kv], dim=0)
+                want = torch.empty_like(got)
+                dist.recv(want, src=t.src_rank)
+                ok = ok and bool(torch.equal(got.view(torch.int16), want.view(torch.int16)))
+        return ok
+
+    def reset_sinks():
+        if not is_src:
+            for layer in kv:
+                layer.view(torch.int16).fill_(0x7FFF)
+        torch.cuda.synchronize(device)
+        dist.barrier()
+
+    def sample_of(plan, sink):
+        """The sampled request of a (wave, sink): its smallest transfer, first 8 blocks."""
+        mine = [t for t in plan.transfers if t.dst_rank == sink]
+        if not mine:
+            return None
+        t = min(mine, key=lambda t: (len(t.src_blocks), t.request_id))
+        return t.src_rank, t.src_blocks[:8], t.dst_blocks[:8]
+
+    def digest(blocks):
+        idx = torch.tensor(blocks, dtype=torch.long, device=device)
+        data = torch.stack([layer[:, idx] for layer in kv], dim=0).view(torch.int16).cpu()
+        return hashlib.sha256(data.numpy().tobytes()).hexdigest()
+
+    verified = {}
+    # 1. the timed path itself (waves in flight two deep): SHA-256 of a sampled request per wave and sink, taken
+    #    when the wave has landed and while later waves are running, against the source's digest of the same blocks
+    landed = {}
+
+    def on_wave_landed(wv):
+        smp = sample_of(plans[wv], rank)
+        if smp is not None:
+            landed[wv] = digest(smp[2])
+
+    res = worker.migrate_waves(plans, ledger("gate"), depth=2, tables=pull_tables, on_wave_landed=on_wave_landed)
+    assert "error" not in res, res
+    expected = {}
+    for wv, plan in enumerate(plans):
+        for d in sinks:
+            smp = sample_of(plan, d)
+            if smp is not None and smp[0] == rank:
+                expected[(wv, d)] = digest(smp[1])
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (expected, landed))
+    want_all = {k: v for e, _ in gathered for k, v in e.items()}
+    ok = all(gathered[d][1].get(wv) == h for (wv, d), h in want_all.items())
+    verified["pull_waves_in_flight_sha256_samples"] = all_true(ok and len(want_all) > 0)
+    sampled = len(want_all)
+    # 2. every request of every wave, bit for bit, for each transport
+    verified_waves = {}
+    for method in ("pull", "alltoall", "nccl"):
+        if method == "alltoall":
+            try:
+                worker.init_native_nccl()
+            except Exception as e:
+                verified[method] = f"unavailable: {type(e).__name__}: {e}"
+                continue
+        reset_sinks()
+        ok, n_ok = True, 0
+        for plan in plans:
+            r = worker.migrate(plan, method=method)
+            good = "error" not in r and verify_wave(plan)
+            ok = ok and good
+            n_ok += 1 if all_true(good) else 0
+        verified[method] = all_true(ok)
+        verified_waves[method] = n_ok
+    verified_all = all(v is True for v in verified.values())
+
+    # ---- reference rates measured in this run --------------------------------------------------------------
+    probe = {}
+    if worker._nccl_comm is not None and rank in (sources[0], sinks[0]):
+        pass  # measured below by both ends
+    one_gib = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+
+    def nccl_pair():
+        if rank == sources[0]:
+            worker.ctx.send_packed(worker._nccl_comm, one_gib, sinks[0])
+        elif rank == sinks[0]:
+            worker.ctx.recv_packed(worker._nccl_comm, one_gib, sources[0])
+
+    if worker._nccl_comm is not None:
+        ms_p = max_ms(timed(nccl_pair, 5, 2, device, barrier))
+        probe["nccl_sendrecv_1gib_gbs"] = round((1 << 30) * 5 / (ms_p / 1e3) / 1e9, 1)
+    del one_gib
+    # one contiguous flow through the copy kernel: the first sink loads the first quarter of the first source's pool
+    quarter = w["NB"] // 4
+    flow_ids = worker.pool.upload_ids(list(range(quarter)))
+
+    def one_flow():
+        if rank == sinks[0]:
+            worker.peer_pools[sources[0]].copy_blocks(worker.pool, flow_ids, flow_ids)
+
+    ms_f = max_ms(timed(one_flow, 3, 1, device, barrier))
+    probe["single_flow_contiguous_pull_gbs"] = round(quarter * block_bytes(w) * 3 / (ms_f / 1e3) / 1e9, 1)
+
+    # ---- timed: headline, end to end -------------------------------------------------------------------------
     l0 = worker.ctx.launch_count
+    wave_times.clear()
     with ClockSampler(local) as clocks:
         ms = max_ms(timed(step_pull, args.steps, args.warmup, device, barrier))
-    launches = worker.ctx.launch_count - l0 - args.warmup * sum(len(p) for p in pull_tables)
+    launches = worker.ctx.launch_count - l0 - args.warmup * sum(len(t) for t in pull_tables)
     lt = torch.tensor([launches], device=device, dtype=torch.int64)
     dist.all_reduce(lt)
     value = payload * args.steps / (ms / 1e3) / 1e9
-
-    # end to end through the worker API with host id lists (tables uploaded inside the timed region)
-    def step_e2e():
-        for plan in plans:
-            res = worker.migrate(plan, method="pull")
-            assert "error" not in res, res
+    # per wave: how far apart the sinks' device times are (mean over the timed steps)
+    mine = [sum(col) / len(col) for col in zip(*wave_times[-args.steps:])] if wave_times and wave_times[-1] else []
+    all_waves = [None] * world
+    dist.all_gather_object(all_waves, mine)
+    per_wave = [[aw[k] for aw in all_waves if len(aw) > k] for k in range(len(plans))]
+    spread = [max(c) - min(c) for c in per_wave if c]
+    longest = [max(c) for c in per_wave if c]
 
     e2e_steps = max(2, args.steps // 4)
     ms_e = max_ms(timed(step_e2e, e2e_steps, 2, device, barrier))
     h2d = sum(8 * len(t.src_blocks) for p in plans for t in p.transfers)
 
     variants = {}
-    line = None
-    if rank == 0:
-        per_src_gbs = value / len(sources)
-        line = {
-            "metric": "kv_migration_payload_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
-            "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
-                       "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(plans),
-                       "payload_gib_per_step": round(payload / GIB, 2), "sources": sources, "sinks": sinks,
-                       "path": "one direct-load kernel per (source, sink) launched by the sink, its sources side by "
-                               "side on separate streams with grids capped to one CTA per SM in total: NVLink loads "
-                               "from the source's peer-mapped pool, local stores", "l2": "inputs larger than L2",
-                       "per_source_egress_gbs": round(per_src_gbs, 2),
-                       "per_sink_ingress_gbs": round(value / len(sinks), 2),
-                       "per_pair_mean_gbs": round(value / (len(sources) * len(sinks)), 2),
-                       "per_sink_ingress_frac_of_900": round(value / len(sinks) / 900.0, 4),
-                       "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
-            "verified_bit_exact_checksum": verified,
-            "roofline": {"bound": "nvlink", "achieved": round(per_src_gbs, 1), "peak": NVLINK_PEER_COPY_GBS,
-                         "unit": "GB/s", "frac": round(per_src_gbs / NVLINK_PEER_COPY_GBS, 4), "traffic": None,
-                         "peak_kind": "of measured peer copy per direction per GPU (900 nominal)",
-                         "frac_of_900_nominal": round(per_src_gbs / 900.0, 4), "kernel": "page_copy_ldg (peer loads)"},
-            "e2e": {"value": round(payload * e2e_steps / (ms_e / 1e3) / 1e9, 2), "unit": "GB/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16 * len(plans) * len(sources),
-                    "api": "V0Worker.migrate(plan, method='pull') with host id lists", "steps": e2e_steps},
-            "gpu_launches": int(lt.item()),
-            "clocks": clocks.summary(),
-            "variants": variants,
-        }
-    def run_variants():
-        nccl_steps = max(2, args.steps // 4)
-        ms_p = max_ms(timed(step_push, nccl_steps, 2, device, barrier))
-        variants["peer_push"] = {"value": round(payload * nccl_steps / (ms_p / 1e3) / 1e9, 2), "unit": "GB/s",
-                                 "ms_per_step": round(ms_p / nccl_steps, 3),
-                                 "path": "sources store into the sinks' peer-mapped pools (same kernel, other direction)"}
+    deadline = t_start + float(os.environ.get("EMM_BENCH_TIME_LIMIT_S", "420"))
+
+    def time_left():
+        """Every rank takes rank 0's view of the clock, so that all skip the same variants."""
+        t = torch.tensor([1 if time.monotonic() < deadline else 0], device=device, dtype=torch.int32)
+        dist.broadcast(t, src=0)
+        return bool(t.item())
+
+    def variant(name, fn, steps, path, extra=None):
+        if not time_left():
+            variants.setdefault("skipped_for_time", []).append(name)
+            return
         try:
-            ms_n = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
-            variants["nccl_staged"] = {"value": round(payload * nccl_steps / (ms_n / 1e3) / 1e9, 2), "unit": "GB/s",
-                                       "ms_per_step": round(ms_n / nccl_steps, 3),
-                                       "path": "pack -> NCCL send/recv -> unpack, layer-chunk pipeline"}
-        except Exception as e:
-            variants["nccl_staged"] = {"error": f"{type(e).__name__}: {e}"}
+            ms_v = max_ms(timed(fn, steps, 2, device, barrier))
+            variants[name] = {"value": round(payload * steps / (ms_v / 1e3) / 1e9, 2), "unit": "GB/s",
+                              "per_source_egress_gbs": round(payload * steps / (ms_v / 1e3) / 1e9 / len(sources), 2),
+                              "ms_per_step": round(ms_v / steps, 3), "path": path}
+            if extra:
+                variants[name].update(extra)
+        except Exception as e:  # a variant is an extra; its failure is reported, the headline stands
+            variants[name] = {"error": f"{type(e).__name__}: {e}"}
 
-        try:  # the same staged pipeline run inside the C library on its own communicator and streams
-            worker.init_native_nccl()
-            ms_nn = max_ms(timed(step_nccl, nccl_steps, 2, device, barrier))
-            variants["nccl_staged_native"] = {"value": round(payload * nccl_steps / (ms_nn / 1e3) / 1e9, 2), "unit": "GB/s",
-                                              "ms_per_step": round(ms_nn / nccl_steps, 3),
-                                              "path": "emm_send_blocks / emm_recv_blocks: pack -> ncclSend, ncclRecv -> "
-                                                      "unpack on library streams"}
-            def step_a2a():
-                for plan in plans:
-                    res = worker.migrate(plan, method="alltoall")
-                    assert "error" not in res, res
-
-            ms_a = max_ms(timed(step_a2a, nccl_steps, 2, device, barrier))
-            variants["nccl_alltoall_pipelined"] = {
-                "value": round(payload * nccl_steps / (ms_a / 1e3) / 1e9, 2), "unit": "GB/s",
-                "ms_per_step": round(ms_a / nccl_steps, 3),
-                "path": "per layer chunk: one gather for all sinks, one grouped ncclSend/ncclRecv exchange among all "
-                        "ranks, one scatter for all sources; three streams, two staging slots"}
-        except Exception as e:
-            variants["nccl_staged_native"] = {"error": f"{type(e).__name__}: {e}"}
-
+    if not args.skip_extras:
+        v_steps = max(2, args.steps // 4)
+        variant("pull_wave_at_a_time", step_method("pull"), v_steps,
+                "the same direct loads with every wave closed by an agreement of all ranks before the next starts")
+        variant("peer_push", step_push_resident, v_steps,
+                "sources store into the sinks' peer-mapped pools (same kernel, other direction), a barrier per wave")
+        if worker._nccl_comm is not None:
+            variant("nccl_alltoall_pipelined", step_method("alltoall"), v_steps,
+                    "per layer chunk: one gather laid out [sink][layer][plane][blocks], one grouped exchange with one "
+                    "ncclSend per sink and one ncclRecv per source, one scatter; three streams, two staging slots",
+                    {"verified_bit_exact": verified.get("alltoall")})
+            variant("nccl_staged", step_method("nccl"), v_steps,
+                    "per pair: emm_send_blocks / emm_recv_blocks, pack -> ncclSend, ncclRecv -> unpack on library streams",
+                    {"verified_bit_exact": verified.get("nccl")})
         # Every rank a source and a sink at once (the rebalancing exchange): rank r loads the lower half of
-        # rank r+1's pool into the upper half of its own. Run last among the device-resident variants because
-        # it overwrites pool contents.
+        # rank r+1's pool into the upper half of its own. Last, because it overwrites pool contents.
         half = w["NB"] // 2
         ring_src = worker.pool.upload_ids(torch.randperm(half, generator=torch.Generator().manual_seed(rank)).tolist())
         ring_dst = worker.pool.upload_ids((torch.randperm(half, generator=torch.Generator().manual_seed(50 + rank)) + half).tolist())
@@ -908,126 +1109,55 @@ def bench_multi(args):
             torch.cuda.synchronize(device)
             dist.barrier()
 
-        ring_steps = max(3, args.steps // 2)
-        ms_r = max_ms(timed(step_ring, ring_steps, 2, device, barrier))
-        ring_bytes = world * half * block_bytes(w)
-        variants["ring_exchange_all_ranks"] = {
-            "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
-            "per_gpu_ingress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
-            "ms_per_step": round(ms_r / ring_steps, 3),
-            "path": "every rank pulls half of the next rank's pool into its own at the same time"}
+        if time_left():
+            ring_steps = max(3, args.steps // 2)
+            ms_r = max_ms(timed(step_ring, ring_steps, 2, device, barrier))
+            ring_bytes = world * half * block_bytes(w)
+            variants["ring_exchange_all_ranks"] = {
+                "value": round(ring_bytes * ring_steps / (ms_r / 1e3) / 1e9, 2), "unit": "GB/s",
+                "per_gpu_ingress_gbs": round(ring_bytes / world * ring_steps / (ms_r / 1e3) / 1e9, 2),
+                "ms_per_step": round(ms_r / ring_steps, 3),
+                "path": "every rank pulls half of the next rank's pool into its own at the same time"}
 
-
-    # The variants are extras: if one of them stalls (an NCCL path on an unusual fabric), the headline
-    # line is still printed and the job ends instead of hanging until an outer limit kills it.
-    done = threading.Event()
-
-    def give_up():
-        if done.is_set():
-            return
-        if rank == 0:
-            variants["timed_out"] = True
-            print(json.dumps(line), flush=True)
-        os._exit(0)
-
-    watchdog = threading.Timer(float(os.environ.get("EMM_BENCH_VARIANT_LIMIT_S", "240")), give_up)
-    watchdog.daemon = True
-    watchdog.start()
-    if not args.skip_extras:
-        run_variants()
-    done.set()
-    watchdog.cancel()
     if rank == 0:
+        per_src_gbs = value / len(sources)
+        line = {
+            "metric": "kv_migration_payload_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+            "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
+                       "requests": w["requests"], "blocks_per_step": total_blocks, "waves": len(plans),
+                       "payload_gib_per_step": round(payload / GIB, 2), "sources": sources, "sinks": sinks,
+                       "path": "one direct-load kernel per (wave, source, sink) launched by the sink, its sources side by "
+                               "side on separate streams with grids capped to one CTA per SM in total: NVLink loads "
+                               "from the source's peer-mapped pool, local stores; waves of half a pool, two in flight, "
+                               "ordered by a completion ledger instead of a barrier", "l2": "inputs larger than L2",
+                       "per_source_egress_gbs": round(per_src_gbs, 2),
+                       "per_sink_ingress_gbs": round(value / len(sinks), 2),
+                       "per_pair_mean_gbs": round(value / (len(sources) * len(sinks)), 2),
+                       "per_sink_ingress_frac_of_900": round(value / len(sinks) / NVLINK_NOMINAL_GBS, 4),
+                       "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1),
+                       "wave_sink_ms": {"longest_mean": round(sum(longest) / max(1, len(longest)), 3),
+                                        "max_minus_min_mean": round(sum(spread) / max(1, len(spread)), 3),
+                                        "max_minus_min_worst": round(max(spread), 3) if spread else None}},
+            "verified_bit_exact": verified_all, "verified_waves": verified_waves, "waves": len(plans),
+            "verified_methods": verified, "verified_sha256_samples": sampled,
+            "verified_how": "before timing: (1) the timed path with two waves in flight, SHA-256 of a sampled request per "
+                            "wave and sink taken while later waves run, against the source's digest; (2) per transport, "
+                            "every request of every wave: the source ships stack(layer[:, src_ids]) through "
+                            "torch.distributed and the sink compares it with stack(layer[:, dst_ids]) by torch.equal",
+            "roofline": {"bound": "nvlink", "achieved": round(per_src_gbs, 1), "peak": NVLINK_NOMINAL_GBS,
+                         "unit": "GB/s", "frac": round(per_src_gbs / NVLINK_NOMINAL_GBS, 4), "traffic": None,
+                         "peak_kind": "of nominal NVLink 5 per direction per GPU (source egress is the bound)",
+                         "measured_in_this_run": probe, "kernel": "page_copy_ldg (peer loads)"},
+            "e2e": {"value": round(payload * e2e_steps / (ms_e / 1e3) / 1e9, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16 * len(sinks),
+                    "api": "V0Worker.migrate_waves(plans, ledger) with host id lists", "steps": e2e_steps},
+            "gpu_launches": int(lt.item()),
+            "clocks": clocks.summary(),
+            "variants": variants,
+        }
         print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
-
-
-def probe_fabric(args):
-    """Peer-copy patterns over NVSwitch (N >= 2 ranks): one flow with different grid sizes, and with
-    N >= 4 two sources -> all other ranks as sinks, pulled side by side with full grids, with grids capped
-    to one CTA per SM in total, and one source at a time. One JSON line per pattern on rank 0. These
-    measurements fixed the schedule V0Worker.migrate uses."""
-    import torch.distributed as dist
-
-    from elasticmm_b200.engine.v0 import V0Worker
-
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
-    torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
-    w = dict(WORKLOADS["llava13b_cfg4"], NB=1024)
-    n = 512  # blocks per flow: 6.25 GiB
-    worker = V0Worker(worker_id=rank, dtype=w["dtype"], device=device, global_rank=rank, world_size=world,
-                      kv_cache=gpu_pool(w, device, rank))
-    worker.init_global_nccl()
-    handles = [None] * world
-    dist.all_gather_object(handles, (worker.get_ipc_handles(), worker.get_pool_desc()))
-    for peer in range(world):
-        if peer != rank:
-            worker.attach_peer_pool(peer, handles[peer][0], handles[peer][1])
-    g = torch.Generator().manual_seed(rank)
-    tabs = {p: (worker.pool.upload_ids(torch.randperm(w["NB"] // 2, generator=g)[:n].tolist()),
-                worker.pool.upload_ids((torch.randperm(w["NB"] // 2, generator=g)[:n] + w["NB"] // 2).tolist()))
-            for p in range(world)}
-    streams = {p: torch.cuda.Stream(device) for p in range(world)}
-    flow_bytes = n * block_bytes(w)
-
-    def run(name, ops, flows, cap=None, serial=False, iters=3):
-        """ops: [(kind, peer)] this rank runs; 'pull' loads peer -> here, 'push' stores here -> peer."""
-        def step():
-            main = torch.cuda.current_stream(device)
-            for kind, peer in ops:
-                st = main if serial else streams[peer]
-                if not serial:
-                    st.wait_stream(main)
-                with torch.cuda.stream(st):
-                    si, di = tabs[peer]
-                    if kind == "pull":
-                        worker.peer_pools[peer].copy_blocks(worker.pool, si, di, max_ctas=cap)
-                    else:
-                        worker.pool.copy_blocks(worker.peer_pools[peer], si, di, max_ctas=cap)
-            if not serial:
-                for _, peer in ops:
-                    main.wait_stream(streams[peer])
-        step()
-        torch.cuda.synchronize(device)
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            step()
-        b.record()
-        torch.cuda.synchronize(device)
-        ms = torch.tensor([a.elapsed_time(b) / iters], device=device, dtype=torch.float64)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        dist.barrier()
-        if rank == 0:
-            print(json.dumps({"probe": name, "flows": flows, "ms": round(ms.item(), 3),
-                              "total_gbs": round(flows * flow_bytes / ms.item() / 1e6, 1)}))
-
-    for cap in (None, 74, 48, 37, 24):
-        run(f"one pull flow 1<-0, grid cap {cap}", [("pull", 0)] if rank == 1 else [], 1, cap=cap)
-        run(f"one push flow 0->1, grid cap {cap}", [("push", 1)] if rank == 0 else [], 1, cap=cap)
-    if world >= 4:
-        srcs, snks = [0, 1], list(range(2, world))
-        j = snks.index(rank) if rank in snks else 0
-        pulls = [("pull", s) for s in srcs] if rank in snks else []
-        run(f"pull 2->{len(snks)}, both sources at once, full grids", pulls, 2 * len(snks))
-        for cap in (120, 100, 74, 48):
-            run(f"pull 2->{len(snks)}, both sources at once, grid cap {cap} each", pulls, 2 * len(snks), cap=cap)
-        run(f"pull 2->{len(snks)}, one source at a time, rotated start",
-            [("pull", srcs[(j + k) % 2]) for k in range(2)] if rank in snks else [], 2 * len(snks), serial=True)
-        run(f"pull 2->{len(snks)}, one source at a time, same start", pulls, 2 * len(snks), serial=True)
-        pushes = [("push", d) for d in snks] if rank in srcs else []
-        run(f"push 2->{len(snks)}, all sinks at once, full grids", pushes, 2 * len(snks))
-        i = srcs.index(rank) if rank in srcs else 0
-        k0 = i * (len(snks) // 2)
-        run(f"push 2->{len(snks)}, one sink at a time, rotated start",
-            [("push", snks[(k0 + k) % len(snks)]) for k in range(len(snks))] if rank in srcs else [],
-            2 * len(snks), serial=True)
-        run("ring: every rank pulls from the next", [("pull", (rank + 1) % world)], world)
-        run("ring: every rank pushes to the next", [("push", (rank + 1) % world)], world)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -1045,14 +1175,6 @@ def main():
                     help="N=1: pool geometry and request mix of the gather -> scatter step (default: the headline one)")
     ap.add_argument("--skip-extras", action="store_true", help="N=1: skip the append and compaction objects")
     ap.add_argument("--skip-cpu", action="store_true", help="N=1: skip the CPU baseline leg")
-    ap.add_argument("--probe-fabric", action="store_true",
-                    help="N>1: measure peer-copy patterns over NVSwitch instead of the migration workload")
-    ap.add_argument("--variant", type=int, default=None, help="copy kernel family (1 bulk, 2 ldg)")
-    ap.add_argument("--chunk", type=int, default=None)
-    ap.add_argument("--stages", type=int, default=None)
-    ap.add_argument("--warps", type=int, default=None)
-    ap.add_argument("--ctas-per-sm", type=int, default=None)
-    ap.add_argument("--unroll", type=int, default=None)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.small:
@@ -1066,16 +1188,7 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
-    from elasticmm_b200 import get_context
-
-    if any(v is not None for v in (args.variant, args.chunk, args.stages, args.warps, args.ctas_per_sm, args.unroll)):
-        dev = int(os.environ.get("LOCAL_RANK", "0"))
-        torch.cuda.set_device(dev)
-        get_context(dev).configure(variant=args.variant, chunk_bytes=args.chunk, stages=args.stages,
-                                   warps=args.warps, ctas_per_sm=args.ctas_per_sm, ldg_unroll=args.unroll)
-    if args.probe_fabric:
-        probe_fabric(args)
-    elif args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         bench_single(args)
     else:
         bench_multi(args)

@@ -47,3 +47,43 @@ def test_measured_peak_fallback(bench, monkeypatch, tmp_path):
     assert bench.measured_peak() == (6650.0, "fallback")
     (tmp_path / "MEASURED_PEAKS.json").write_text('{"hbm_gbs": 6553.3}')
     assert bench.measured_peak() == (6553.3, "measured")
+
+
+def test_build_requests_is_seeded_and_tables_do_not_repeat_within_a_wave(bench):
+    w1 = bench.WORKLOADS["llama7b_cfg1"]
+    counts, waves, reqs = bench.build_requests(w1, 1)
+    assert (counts, waves, reqs) == bench.build_requests(w1, 1)
+    assert len(reqs) == 64 and [len(s) for s, _ in reqs] == [counts[i] for wave in waves for i in wave]
+    pos = 0
+    for wave in waves:
+        src = [b for s, _ in reqs[pos:pos + len(wave)] for b in s]
+        dst = [b for _, d in reqs[pos:pos + len(wave)] for b in d]
+        assert len(set(src)) == len(src) and len(set(dst)) == len(dst)
+        assert all(len(s) == len(d) for s, d in reqs[pos:pos + len(wave)])
+        pos += len(wave)
+
+
+@pytest.mark.parametrize("sources,sinks", [([0, 1], [2, 3]), ([0, 1], [2, 3, 4, 5, 6, 7])])
+def test_wave_plans_use_half_pools_alternately_and_balance_the_sinks(bench, sources, sinks):
+    w = bench.WORKLOADS["llava13b_cfg4"]
+    plans = bench.build_wave_plans(w, sources, sinks)
+    counts = bench.request_blocks(w, 4)
+    half = w["NB"] // 2
+    seen = sorted(int(t.request_id[3:]) for p in plans for t in p.transfers)
+    assert seen == list(range(len(counts)))                               # every request exactly once
+    for k, plan in enumerate(plans):
+        lo, hi = (k % 2) * half, (k % 2) * half + half
+        plan.validate(lambda r: w["NB"])                                   # ranges, no destination block twice
+        for s in sources:
+            used = [b for t in plan.transfers if t.src_rank == s for b in t.src_blocks]
+            assert len(set(used)) == len(used) <= half and all(lo <= b < hi for b in used)
+        for d in sinks:
+            used = [b for t in plan.transfers if t.dst_rank == d for b in t.dst_blocks]
+            assert len(used) <= half and all(lo <= b < hi for b in used)
+    # full waves: all but the last use nearly all of every source's half pool, and no sink has to take in more
+    # per wave than a source sends out (a sink's link then never limits the wave)
+    for plan in plans[:-1]:
+        for s in sources:
+            assert sum(len(t.src_blocks) for t in plan.transfers if t.src_rank == s) > 0.98 * half
+        for d in sinks:
+            assert sum(len(t.src_blocks) for t in plan.transfers if t.dst_rank == d) <= half

@@ -1,5 +1,8 @@
 """Prefill -> decode migration between GPUs (one process per GPU, NCCL + peer-mapped pools).
-Skipped on a box with a single GPU."""
+The NCCL cases need two or four GPUs. The direct-load path (the default migration path) is
+also run as two processes sharing ONE GPU, with a gloo group for the host-side agreement and
+CUDA IPC between the processes, so that a single-GPU box still checks plan-level pulls, waves
+without a barrier and the all-ranks error agreement against the oracle."""
 import os
 import socket
 import tempfile
@@ -204,8 +207,176 @@ def _worker_main(rank, world, port, out_dir):
     results["exchange_exact"] = same(sink, expect(mine))
     dist.barrier()
 
+    results.update(_waves_and_agreement(rank, world, dev, fresh))
     torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
     dist.destroy_process_group()
+
+
+def _wave_plans(n_waves, seed):
+    """Rank 0 -> rank 1 in waves that alternate between the halves of both pools."""
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer
+
+    g = torch.Generator().manual_seed(seed)
+    half = GEOM["NB"] // 2
+    plans = []
+    for wv in range(n_waves):
+        base = (wv % 2) * half
+        sperm = (torch.randperm(half, generator=g) + base).tolist()
+        dperm = (torch.randperm(half, generator=g) + base).tolist()
+        plan, pos = MigrationPlan(), 0
+        for r in range(3):
+            n = int(torch.randint(5, 70, (1,), generator=g))
+            plan.add(Transfer(f"w{wv}r{r}", 0, 1, tuple(sperm[pos:pos + n]), tuple(dperm[pos:pos + n])))
+            pos += n
+        plans.append(plan)
+    return plans
+
+
+def _waves_and_agreement(rank, world, dev, fresh):
+    """Shared by the two-GPU run and the two-processes-on-one-GPU run: direct-load migration per plan,
+    waves two deep without a barrier, and a host-side failure on one rank reported by all."""
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer
+    from elasticmm_b200.engine.v0.transport import WaveLedger
+    from oracle import kv_oracle
+
+    results = {}
+    store = dist.distributed_c10d._get_default_store()
+
+    def mapped(seed, guard):
+        w, cpu = fresh(seed, guard)
+        hs = [None] * world
+        dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
+        for peer in range(world):
+            if peer != rank:
+                w.attach_peer_pool(peer, hs[peer][0], hs[peer][1])
+        return w, cpu
+
+    src_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 70)
+
+    def same(w, want):
+        return all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, want))
+
+    # waves two deep, no barrier between them; every landed wave is checked while the next ones run
+    plans = _wave_plans(5, seed=21)
+    w, _ = mapped(70 if rank == 0 else 0, guard=rank != 0)
+    checked = []
+
+    def on_wave_landed(wv):
+        for t in plans[wv].transfers:
+            got = w.extract_kv_blocks(list(t.dst_blocks)).cpu()
+            checked.append(kv_oracle.bit_equal(got, kv_oracle.extract_kv_blocks(src_cpu, list(t.src_blocks))))
+
+    res = w.migrate_waves(plans, WaveLedger(store, "test/waves"), depth=2,
+                          on_wave_landed=on_wave_landed if rank == 1 else None)
+    results["waves_ok"] = "error" not in res and res["blocks"] == (sum(p.total_blocks() for p in plans) if rank == 1 else 0)
+    if rank == 1:
+        want = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0, fill="guard")
+        for plan in plans:
+            for t in plan.transfers:
+                kv_oracle.write_kv_blocks(want, list(t.dst_blocks), kv_oracle.extract_kv_blocks(src_cpu, list(t.src_blocks)))
+        results["waves_exact"] = same(w, want) and len(checked) == 15 and all(checked) and len(res["wave_ms"]) == 5
+    else:
+        ledger = WaveLedger(store, "test/waves")
+        results["waves_exact"] = all(ledger.count(wv, 0) == 1 for wv in range(5))  # the source saw every wave complete
+    dist.barrier()
+
+    # the same tables resident on the device
+    w2, _ = mapped(70 if rank == 0 else 0, guard=rank != 0)
+    tables = [{0: tuple(w2.pool.upload_ids(t) for t in plan.tables(0, 1))} if rank == 1 else {} for plan in plans]
+    res = w2.migrate_waves(plans, WaveLedger(store, "test/waves_dev"), depth=2, tables=tables)
+    results["waves_device_tables_ok"] = "error" not in res
+    if rank == 1:
+        results["waves_device_tables_exact"] = same(w2, want)
+    dist.barrier()
+
+    # a rank whose peer pool is not mapped: every rank returns the error, nobody hangs, nothing is written
+    w3, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)   # no attach_peer_pool on any rank
+    res = w3.migrate(MigrationPlan([Transfer("r", 0, 1, (1, 2, 3), (4, 5, 6))]), method="pull")
+    results["unmapped_error_on_every_rank_ok"] = "error" in res and res["bytes"] == 0
+    res = w3.migrate_waves(plans, WaveLedger(store, "test/waves_err"))
+    results["unmapped_waves_error_on_every_rank_ok"] = "error" in res
+    bad = MigrationPlan([Transfer("r", 0, 1, (1, 2), (4, GEOM["NB"]))])   # destination id outside the sink's pool
+    res = w.migrate(bad, method="pull")
+    results["bad_id_error_on_every_rank_ok"] = "error" in res
+    if rank == 1:
+        guard = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0, fill="guard")
+        results["unmapped_nothing_written_exact"] = same(w3, guard)
+    dist.barrier()
+    return results
+
+
+def _one_gpu_worker_main(rank, world, port, out_dir):
+    """Two processes on cuda:0. gloo carries the host-side agreement (NCCL refuses two ranks on one GPU);
+    the pools are shared through CUDA IPC exactly as between GPUs, and the sink's kernel loads from the
+    source process's pool. The kernels never wait for one another, so sharing the GPU is safe."""
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import MigrationPlan, Transfer, TransferMethod, V0KVTransferManager, V0Worker
+    from oracle import kv_oracle
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def fresh(seed, guard):
+        cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, seed,
+                                  fill="guard" if guard else "normal")
+        w = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
+                     kv_cache=[t.to(dev) for t in cpu])
+        assert w.init_global_nccl()
+        return w, cpu
+
+    results = _waves_and_agreement(rank, world, dev, fresh)
+
+    # plan level through the manager (transfer_many -> migrate -> one direct-load kernel on the sink)
+    reqs = _requests(3)
+    w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+    hs = [None] * world
+    dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
+    w.attach_peer_pool(1 - rank, hs[1 - rank][0], hs[1 - rank][1])
+    mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
+    mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+    plan = MigrationPlan([Transfer(rid, 0, 1, tuple(s), tuple(d)) for rid, s, d in reqs])
+    launches = w.ctx.launch_count
+    results["transfer_many_ok"] = mgr.transfer_many(plan) and (w.ctx.launch_count - launches) == (1 if rank == 1 else 0)
+    if rank == 1:
+        src_cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 70)
+        want = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16, 0, fill="guard")
+        for _, s, d in reqs:
+            kv_oracle.write_kv_blocks(want, d, kv_oracle.extract_kv_blocks(src_cpu, s))
+        results["transfer_many_exact"] = all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, want))
+    dist.barrier()
+    # push direction and the request-by-request form of the reference's manager call
+    for direction in ("pull", "push"):
+        w, _ = fresh(70 if rank == 0 else 0, guard=rank != 0)
+        hs = [None] * world
+        dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
+        w.attach_peer_pool(1 - rank, hs[1 - rank][0], hs[1 - rank][1])
+        mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER, peer_direction=direction)
+        mgr.register_worker(rank, w, "prefill" if rank == 0 else "decoding")
+        dist.barrier()
+        results[f"per_request_{direction}_ok"] = all(mgr.transfer_kv_cache_sync(rid, 0, 1, s, d) for rid, s, d in reqs)
+        dist.barrier()
+        if rank == 1:
+            results[f"per_request_{direction}_exact"] = all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, want))
+        dist.barrier()
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_sharing_one_gpu_pull_migration_is_bit_exact():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_one_gpu_worker_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        r0, r1 = torch.load(os.path.join(d, "r0.pt")), torch.load(os.path.join(d, "r1.pt"))
+    assert len(r1) >= 14
+    for r in (r0, r1):
+        for k, v in r.items():
+            assert v is True, f"{k} failed: {r}"
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -255,14 +426,16 @@ def _worker4_main(rank, world, port, out_dir):
     plan = _plan4(11)
     plan.validate(lambda r: GEOM["NB"])
     results = {}
-    for method in ("pull", "push", "nccl"):
+    for method in ("pull", "push", "nccl", "alltoall", "waves"):
         is_src = rank < 2
         cpu = kv_oracle.make_pool(GEOM["L"], GEOM["NB"], GEOM["BS"], GEOM["H"], GEOM["D"], torch.bfloat16,
                                   80 + rank if is_src else 0, fill="normal" if is_src else "guard")
         w = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
                      kv_cache=[t.to(dev) for t in cpu])
         w.init_global_nccl()
-        if method != "nccl":
+        if method == "alltoall":
+            w.init_native_nccl()
+        if method not in ("nccl", "alltoall"):
             hs = [None] * world
             dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
             for peer in range(world):
@@ -272,6 +445,13 @@ def _worker4_main(rank, world, port, out_dir):
             mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
             mgr.register_worker(rank, w, "prefill" if is_src else "decoding")
             results[f"{method}_ok"] = mgr.transfer_many(plan)
+        elif method == "waves":  # the plan's transfers as three waves over disjoint blocks, two in flight
+            from elasticmm_b200.engine.v0 import MigrationPlan
+            from elasticmm_b200.engine.v0.transport import WaveLedger
+
+            ledger = WaveLedger(dist.distributed_c10d._get_default_store(), "test4/waves")
+            waves = [MigrationPlan(plan.transfers[k::3]) for k in range(3)]
+            results[f"{method}_ok"] = "error" not in w.migrate_waves(waves, ledger, depth=2)
         else:
             results[f"{method}_ok"] = "error" not in w.migrate(plan, method=method)
         dist.barrier()
