@@ -101,6 +101,9 @@ struct emm_ctx {
   int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
   int l2_hint = 0;                    // bulk family: bit 0 loads, bit 1 stores carry an L2 evict-first hint
   uint64_t wait_limit_ns = emm::kDefaultWaitLimitNs;  // bulk family: bound of each device-side wait
+  int append_variant = 0;      // 0 automatic, 1 one warp per row, 2 segment-granular grid
+  int append_unroll = 0;       // segment variant: items in flight per warp (0 = sized from the work)
+  int append_ctas_per_sm = 0;  // segment variant: resident CTAs per SM the grid is capped at (0 = 8)
   IdSlot ring[kRingSlots];
   int next_slot = 0;
   std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
@@ -574,6 +577,19 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       if (value < 0 || value > 3) return fail(EMM_ERR_BAD_ARG, "L2 hint must be in [0, 3]");
       ctx->l2_hint = (int)value;
       return EMM_OK;
+    case EMM_OPT_APPEND_VARIANT:
+      if (value < 0 || value > 2) return fail(EMM_ERR_BAD_ARG, "append variant must be 0, 1 or 2");
+      ctx->append_variant = (int)value;
+      return EMM_OK;
+    case EMM_OPT_APPEND_UNROLL:
+      if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+        return fail(EMM_ERR_BAD_ARG, "append unroll must be 0, 1, 2, 4 or 8");
+      ctx->append_unroll = (int)value;
+      return EMM_OK;
+    case EMM_OPT_APPEND_CTAS_PER_SM:
+      if (value < 0 || value > 8) return fail(EMM_ERR_BAD_ARG, "append CTAs per SM must be in [0, 8]");
+      ctx->append_ctas_per_sm = (int)value;
+      return EMM_OK;
     case EMM_OPT_WAIT_LIMIT_NS:
       if (value < 1000 || value > 60000000000ll)
         return fail(EMM_ERR_BAD_ARG, "wait limit must be between 1 us and 60 s (in ns)");
@@ -602,6 +618,9 @@ int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
     case EMM_OPT_REMOTE_VARIANT: *value = ctx->remote_variant; return EMM_OK;
     case EMM_OPT_L2_HINT: *value = ctx->l2_hint; return EMM_OK;
     case EMM_OPT_WAIT_LIMIT_NS: *value = (int64_t)ctx->wait_limit_ns; return EMM_OK;
+    case EMM_OPT_APPEND_VARIANT: *value = ctx->append_variant; return EMM_OK;
+    case EMM_OPT_APPEND_UNROLL: *value = ctx->append_unroll; return EMM_OK;
+    case EMM_OPT_APPEND_CTAS_PER_SM: *value = ctx->append_ctas_per_sm; return EMM_OK;
     default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
 }
@@ -987,17 +1006,54 @@ static int append_prepare(emm_pool *pool, int32_t layer_begin, int32_t layer_cou
   return EMM_OK;
 }
 
-// Launches append_rows for prepared arguments. Call with the context's device current.
+}  // extern "C"
+
+template <typename V>
+static void launch_append_segments(emm_ctx *ctx, const emm::AppendArgs &a, cudaStream_t st) {
+  const uint32_t row_vecs = a.row_bytes / (uint32_t)sizeof(V);
+  const uint32_t segs_per_row = (row_vecs + 31u) / 32u;
+  const uint64_t rows = (uint64_t)a.layer_count * (uint64_t)a.num_tokens * 2ull;
+  const uint64_t total = rows * segs_per_row;
+  const int per_sm = ctx->append_ctas_per_sm > 0 ? ctx->append_ctas_per_sm : 8;
+  const uint64_t cap = (uint64_t)ctx->sm_count * per_sm;  // CTAs resident at once
+  int unroll = ctx->append_unroll;
+  if (unroll <= 0) {
+    // as few items per warp as keep the whole job in one resident wave
+    const uint64_t per_warp = (total + cap * emm::kAppendWarps - 1) / (cap * emm::kAppendWarps);
+    unroll = per_warp <= 1 ? 1 : per_warp <= 2 ? 2 : per_warp <= 4 ? 4 : 8;
+  }
+  const uint64_t want = (total + (uint64_t)emm::kAppendWarps * unroll - 1) / ((uint64_t)emm::kAppendWarps * unroll);
+  const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>(want, cap));
+  const int block = emm::kAppendWarps * 32;
+  switch (unroll) {
+    case 1: emm::append_segments<V, 1><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
+    case 2: emm::append_segments<V, 2><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
+    case 4: emm::append_segments<V, 4><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
+    default: emm::append_segments<V, 8><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
+  }
+}
+
+extern "C" {
+
+// Launches the append kernel for prepared arguments. Call with the context's device current.
 static int append_launch(emm_ctx *ctx, const emm::AppendArgs &a, uint32_t align, cudaStream_t st) {
   if (a.num_tokens == 0 || a.layer_count == 0) return EMM_OK;
   const uint64_t rows = (uint64_t)a.layer_count * (uint64_t)a.num_tokens * 2ull;
-  const int grid = (int)((rows + emm::kAppendWarps - 1) / emm::kAppendWarps);
-  const int block = emm::kAppendWarps * 32;
-  if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
-  else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
-  else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
-  else if (align >= 2) emm::append_rows<uint16_t, 4><<<grid, block, 0, st>>>(a);
-  else emm::append_rows<uint8_t, 4><<<grid, block, 0, st>>>(a);
+  if (ctx->append_variant == 2) {
+    if (align >= 16) launch_append_segments<uint4>(ctx, a, st);
+    else if (align >= 8) launch_append_segments<uint2>(ctx, a, st);
+    else if (align >= 4) launch_append_segments<uint32_t>(ctx, a, st);
+    else if (align >= 2) launch_append_segments<uint16_t>(ctx, a, st);
+    else launch_append_segments<uint8_t>(ctx, a, st);
+  } else {
+    const int grid = (int)((rows + emm::kAppendWarps - 1) / emm::kAppendWarps);
+    const int block = emm::kAppendWarps * 32;
+    if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
+    else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
+    else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
+    else if (align >= 2) emm::append_rows<uint16_t, 4><<<grid, block, 0, st>>>(a);
+    else emm::append_rows<uint8_t, 4><<<grid, block, 0, st>>>(a);
+  }
   EMM_CUDA(cudaGetLastError());
   ctx->launches += 1;
   return EMM_OK;

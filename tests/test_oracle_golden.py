@@ -137,3 +137,29 @@ def test_vision_block_transfer_restatement():
     for s, d in zip([7, 0, 11], [2, 8, 5]):
         assert kv_oracle.bit_equal(dst[d], src[s])
     assert torch.count_nonzero(dst[[0, 1, 3, 4, 6, 7]]) == 0
+
+
+APPEND_GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "append_golden.npz"))
+
+
+@pytest.mark.parametrize("case", cases.APPEND_CASES, ids=lambda c: c["name"])
+@pytest.mark.parametrize("impl", ["torch", "c"])
+def test_append_matches_vllm_cache_op(case, impl):
+    """reshape_and_cache of both restatements against pools written by vLLM's own
+    reshape_and_cache_flash (the op behind the reference's model_runner.execute_model,
+    elasticmm/engine/v0/worker_steps.py:281,438), recorded by tests/golden/make_append_golden.py."""
+    pool, key, value, slots = cases.build_append_inputs(case)
+    for l in range(case["L"]):
+        if impl == "torch":
+            kv_oracle.reshape_and_cache(key[l], value[l], pool[l], slots)
+        else:
+            kv_oracle_c.append(pool[l], key[l], value[l], slots)
+    whole = torch.stack(pool, dim=0)
+    name = case["name"]
+    assert sha(whole) == APPEND_GOLDEN[f"{name}/pool_sha256"].tobytes()
+    if case["store"] == "full":
+        assert np.array_equal(kv_oracle.bits(whole).numpy(), APPEND_GOLDEN[f"{name}/pool"])
+
+
+def test_append_fixture_names_the_vllm_version_that_made_it():
+    assert bytes(APPEND_GOLDEN["vllm_version"]).decode().startswith("0.")
