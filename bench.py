@@ -665,6 +665,26 @@ def bench_append(ctx, device, args):
     out["all_layers_call"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
                               "launches_per_step": 1, "hbm_gbs": round(algo * steps / (ms / 1e3) / 1e9, 1),
                               "frac_of_peak": round(algo * steps / (ms / 1e3) / 1e9 / peak, 4), "peak_kind": f"of {kind}"}
+    # the same launches replayed from a CUDA graph (16 steps on rotating buffers per graph): the kernel's own
+    # rate, without the host time of the Python call between launches
+    try:
+        stream = torch.cuda.Stream(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            all_layers()
+            stream.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(16):
+                    all_layers()
+        reps = max(4, steps // 4)
+        ms = timed(graph.replay, reps, 3, device)
+        n = reps * 16
+        out["all_layers_graph_replay"] = {"tokens_per_s": round(T * n / (ms / 1e3)), "us_per_step": round(ms * 1e3 / n, 2),
+                                          "launches_per_step": 1, "hbm_gbs": round(algo * n / (ms / 1e3) / 1e9, 1),
+                                          "frac_of_peak": round(algo * n / (ms / 1e3) / 1e9 / peak, 4),
+                                          "peak_kind": f"of {kind}"}
+    except Exception as e:
+        out["all_layers_graph_replay"] = {"error": f"{type(e).__name__}: {e}"}
     ms = timed(per_layer, steps, 5, device)
     out["per_layer_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)), "us_per_step": round(ms * 1e3 / steps, 2),
                               "launches_per_step": L}
@@ -676,8 +696,10 @@ def bench_append(ctx, device, args):
         slot_buf.copy_(maps[it["i"] % 16])
         it["i"] += 1
         stream = torch.cuda.current_stream(device).cuda_stream
+        launch = bound.raw
         for l in range(L):
-            bound(l, stream)
+            if launch(l, stream):
+                bound(l, stream)  # raises with the library's message
 
     ms = timed(per_layer_bound, steps, 5, device)
     out["per_layer_bound_calls"] = {"tokens_per_s": round(T * steps / (ms / 1e3)),

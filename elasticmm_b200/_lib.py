@@ -45,9 +45,7 @@ OPT_MAX_CTAS = 6
 OPT_REMOTE_VARIANT = 7
 OPT_L2_HINT = 8
 OPT_WAIT_LIMIT_NS = 9
-OPT_APPEND_VARIANT = 10
-OPT_APPEND_UNROLL = 11
-OPT_APPEND_CTAS_PER_SM = 12
+OPT_PDL = 10
 
 
 class PoolDesc(C.Structure):

@@ -101,9 +101,7 @@ struct emm_ctx {
   int remote_variant = EMM_COPY_LDG;  // family used when a side is peer or host memory
   int l2_hint = 0;                    // bulk family: bit 0 loads, bit 1 stores carry an L2 evict-first hint
   uint64_t wait_limit_ns = emm::kDefaultWaitLimitNs;  // bulk family: bound of each device-side wait
-  int append_variant = 0;      // 0 automatic, 1 one warp per row, 2 segment-granular grid
-  int append_unroll = 0;       // segment variant: items in flight per warp (0 = sized from the work)
-  int append_ctas_per_sm = 0;  // segment variant: resident CTAs per SM the grid is capped at (0 = 8)
+  int pdl = 1;                 // copy kernels are launched with programmatic stream serialisation
   IdSlot ring[kRingSlots];
   int next_slot = 0;
   std::vector<uint64_t> bitmap;  // scratch for duplicate / overlap checks
@@ -309,7 +307,8 @@ void launch_ldg(emm_ctx *ctx, const PageCopyArgs &a, int grid, uint32_t align, c
 // both sides are ordinary memory of this GPU.
 int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_t layer_begin,
                      int32_t layer_count, int64_t page_bytes, uint32_t align, bool local,
-                     cudaStream_t st, int planes = 2, uint32_t tx_overcount = 0) {
+                     cudaStream_t st, int planes = 2, uint32_t tx_overcount = 0,
+                     const int64_t *inline_src = nullptr, const int64_t *inline_dst = nullptr) {
   if (n == 0 || layer_count == 0) return EMM_OK;
   DeviceGuard guard(ctx->device);
   if (!guard.ok()) return fail(EMM_ERR_CUDA, "cannot select device %d", ctx->device);
@@ -331,6 +330,19 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
   a.status = ctx->d_status;
   a.wait_limit_ns = ctx->wait_limit_ns;
   a.tx_overcount = tx_overcount;
+  a.inline_count = 0;
+  a.src_inline = a.dst_inline = 0;
+  if ((inline_src || inline_dst) && n <= emm::kInlineIds) {
+    a.inline_count = (uint32_t)n;
+    if (inline_src) {
+      a.src_inline = 1;
+      for (int32_t i = 0; i < n; ++i) a.inline_ids[0][i] = (int32_t)inline_src[i];
+    }
+    if (inline_dst) {
+      a.dst_inline = 1;
+      for (int32_t i = 0; i < n; ++i) a.inline_ids[1][i] = (int32_t)inline_dst[i];
+    }
+  }
   const bool segmented = src.seg_prefix != nullptr || dst.seg_prefix != nullptr;
 
   int64_t chunk = ctx->chunk_bytes;
@@ -372,10 +384,21 @@ int launch_page_copy(emm_ctx *ctx, CopySide src, CopySide dst, int32_t n, int32_
     uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
     if (ctx->max_ctas > 0) cap = std::min<uint64_t>(cap, ctx->max_ctas);
     const int grid = (int)std::min<uint64_t>(want, cap);
-    if (segmented)
-      emm::page_copy_bulk<true><<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
-    else
-      emm::page_copy_bulk<false><<<grid, warps * 32, smem, st>>>(a, (uint32_t)ctx->stages, (uint32_t)ctx->l2_hint);
+    // Launched with programmatic stream serialisation: when the previous kernel in the stream is another
+    // copy of this library, this grid's CTAs are placed and set up their rings while that one drains.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)(warps * 32));
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    const uint32_t stages_arg = (uint32_t)ctx->stages, hint_arg = (uint32_t)ctx->l2_hint;
+    if (segmented) EMM_CUDA(cudaLaunchKernelEx(&cfg, emm::page_copy_bulk<true>, a, stages_arg, hint_arg));
+    else EMM_CUDA(cudaLaunchKernelEx(&cfg, emm::page_copy_bulk<false>, a, stages_arg, hint_arg));
   } else {
     // A copy to or from a peer GPU or pinned host memory is bound by the link, not
     // by HBM: 48 CTAs already saturate NVLink (measured), and side-by-side copies
@@ -410,7 +433,7 @@ int check_layer_range(const emm_pool *p, int32_t begin, int32_t count) {
 int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t layer_count,
                 const int32_t *d_ids, int32_t n, const void *d_packed, uint64_t packed_bytes,
                 void *stream, const uint32_t *d_seg_prefix = nullptr, int32_t num_segs = 0,
-                uint32_t tx_overcount = 0) {
+                uint32_t tx_overcount = 0, const int64_t *h_inline_ids = nullptr) {
   const char *what = to_packed ? "gather" : "scatter";
   if (int rc = check_pool_for_pages(pool, what)) return rc;
   if (int rc = check_layer_range(pool, layer_begin, layer_count)) return rc;
@@ -420,7 +443,7 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
     return fail(EMM_ERR_LENGTH, "%s: packed buffer holds %llu bytes, %d blocks need %llu", what,
                 (unsigned long long)packed_bytes, n, (unsigned long long)want);
   if (n == 0 || layer_count == 0) return EMM_OK;
-  if (!d_ids || !d_packed) return fail(EMM_ERR_BAD_ARG, "%s: null pointer", what);
+  if ((!d_ids && !h_inline_ids) || !d_packed) return fail(EMM_ERR_BAD_ARG, "%s: null pointer", what);
   const uint32_t align = std::min(pool->align, pow2_align((uint64_t)d_packed));
   if (align < (uint32_t)pool->desc.elem_size)
     return fail(EMM_ERR_ALIGN, "%s: packed buffer not aligned to elem_size", what);
@@ -434,10 +457,10 @@ int packed_copy(emm_pool *pool, bool to_packed, int32_t layer_begin, int32_t lay
   if (tx_overcount && align < 16) return fail(EMM_ERR_ALIGN, "%s: the wait test needs 16-byte granular pages", what);
   return to_packed ? launch_page_copy(pool->ctx, ps, bs, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream, pool->planes, tx_overcount)
+                                      (cudaStream_t)stream, pool->planes, tx_overcount, h_inline_ids, nullptr)
                    : launch_page_copy(pool->ctx, bs, ps, n, layer_begin, layer_count,
                                       pool->page_bytes, align, pool->device_local,
-                                      (cudaStream_t)stream, pool->planes, tx_overcount);
+                                      (cudaStream_t)stream, pool->planes, tx_overcount, nullptr, h_inline_ids);
 }
 
 // Uploads host ids (already validated) into a ring slot; returns the device
@@ -577,18 +600,9 @@ int emm_ctx_set_option(emm_ctx *ctx, int option, int64_t value) {
       if (value < 0 || value > 3) return fail(EMM_ERR_BAD_ARG, "L2 hint must be in [0, 3]");
       ctx->l2_hint = (int)value;
       return EMM_OK;
-    case EMM_OPT_APPEND_VARIANT:
-      if (value < 0 || value > 2) return fail(EMM_ERR_BAD_ARG, "append variant must be 0, 1 or 2");
-      ctx->append_variant = (int)value;
-      return EMM_OK;
-    case EMM_OPT_APPEND_UNROLL:
-      if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
-        return fail(EMM_ERR_BAD_ARG, "append unroll must be 0, 1, 2, 4 or 8");
-      ctx->append_unroll = (int)value;
-      return EMM_OK;
-    case EMM_OPT_APPEND_CTAS_PER_SM:
-      if (value < 0 || value > 8) return fail(EMM_ERR_BAD_ARG, "append CTAs per SM must be in [0, 8]");
-      ctx->append_ctas_per_sm = (int)value;
+    case EMM_OPT_PDL:
+      if (value != 0 && value != 1) return fail(EMM_ERR_BAD_ARG, "PDL option must be 0 or 1");
+      ctx->pdl = (int)value;
       return EMM_OK;
     case EMM_OPT_WAIT_LIMIT_NS:
       if (value < 1000 || value > 60000000000ll)
@@ -618,9 +632,7 @@ int emm_ctx_get_option(emm_ctx *ctx, int option, int64_t *value) {
     case EMM_OPT_REMOTE_VARIANT: *value = ctx->remote_variant; return EMM_OK;
     case EMM_OPT_L2_HINT: *value = ctx->l2_hint; return EMM_OK;
     case EMM_OPT_WAIT_LIMIT_NS: *value = (int64_t)ctx->wait_limit_ns; return EMM_OK;
-    case EMM_OPT_APPEND_VARIANT: *value = ctx->append_variant; return EMM_OK;
-    case EMM_OPT_APPEND_UNROLL: *value = ctx->append_unroll; return EMM_OK;
-    case EMM_OPT_APPEND_CTAS_PER_SM: *value = ctx->append_ctas_per_sm; return EMM_OK;
+    case EMM_OPT_PDL: *value = ctx->pdl; return EMM_OK;
     default: return fail(EMM_ERR_BAD_ARG, "unknown option %d", option);
   }
 }
@@ -839,8 +851,10 @@ int emm_scatter_many_layers(emm_pool *pool, int32_t layer_begin, int32_t layer_c
                    packed_bytes, stream);
 }
 
-int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
-                    const int32_t *d_dst_ids, int32_t n, void *stream) {
+}  // extern "C"
+
+static int copy_blocks_impl(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids, const int32_t *d_dst_ids,
+                            const int64_t *h_src_inline, const int64_t *h_dst_inline, int32_t n, void *stream) {
   if (int rc = check_pool_for_pages(src, "copy_blocks(src)")) return rc;
   if (int rc = check_pool_for_pages(dst, "copy_blocks(dst)")) return rc;
   if (src->ctx != dst->ctx) return fail(EMM_ERR_BAD_ARG, "copy_blocks: pools of different contexts");
@@ -851,10 +865,19 @@ int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
                 dst->desc.num_layers);
   if (n < 0) return fail(EMM_ERR_BAD_ARG, "copy_blocks: negative block count");
   if (n == 0) return EMM_OK;
-  if (!d_src_ids || !d_dst_ids) return fail(EMM_ERR_BAD_ARG, "copy_blocks: null id table");
+  if ((!d_src_ids || !d_dst_ids) && (!h_src_inline || !h_dst_inline))
+    return fail(EMM_ERR_BAD_ARG, "copy_blocks: null id table");
   return launch_page_copy(src->ctx, pool_side(src, d_src_ids), pool_side(dst, d_dst_ids), n, 0,
                           src->desc.num_layers, src->page_bytes, std::min(src->align, dst->align),
-                          src->device_local && dst->device_local, (cudaStream_t)stream, src->planes);
+                          src->device_local && dst->device_local, (cudaStream_t)stream, src->planes, 0,
+                          h_src_inline, h_dst_inline);
+}
+
+extern "C" {
+
+int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
+                    const int32_t *d_dst_ids, int32_t n, void *stream) {
+  return copy_blocks_impl(src, dst, d_src_ids, d_dst_ids, nullptr, nullptr, n, stream);
 }
 
 int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed,
@@ -864,6 +887,9 @@ int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed
   if (n > 0 && !h_ids) return fail(EMM_ERR_BAD_ARG, "gather: null id list");
   if (int rc = check_ids_host(h_ids, n, pool->desc.num_blocks, "gather")) return rc;
   if (n == 0) return packed_copy(pool, true, 0, pool->desc.num_layers, nullptr, 0, d_packed, packed_bytes, stream);
+  if (n <= emm::kInlineIds)  // a short table rides in the kernel arguments: no staging copy
+    return packed_copy(pool, true, 0, pool->desc.num_layers, nullptr, n, d_packed, packed_bytes, stream, nullptr, 0, 0,
+                       h_ids);
   DeviceGuard guard(pool->ctx->device);
   IdSlot *slot;
   const int32_t *d_ids;
@@ -886,6 +912,9 @@ int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d
   const bool unique = bitmap_mark(ctx->bitmap, h_ids, n, &dup);
   bitmap_clear(ctx->bitmap, h_ids, n);
   if (!unique) return fail(EMM_ERR_DUPLICATE, "scatter: destination id %lld appears twice", (long long)dup);
+  if (n <= emm::kInlineIds)
+    return packed_copy(pool, false, 0, pool->desc.num_layers, nullptr, n, d_packed, packed_bytes, stream, nullptr, 0,
+                       0, h_ids);
   DeviceGuard guard(ctx->device);
   IdSlot *slot;
   const int32_t *d_ids;
@@ -925,6 +954,7 @@ int emm_copy_blocks_h(emm_pool *src, emm_pool *dst, const int64_t *h_src_ids,
   }
   bitmap_clear(ctx->bitmap, h_dst_ids, n);
   if (rc_check) return rc_check;
+  if (n <= emm::kInlineIds) return copy_blocks_impl(src, dst, nullptr, nullptr, h_src_ids, h_dst_ids, n, stream);
   DeviceGuard guard(ctx->device);
   IdSlot *slot;
   const int32_t *d_s, *d_d;
@@ -1006,54 +1036,17 @@ static int append_prepare(emm_pool *pool, int32_t layer_begin, int32_t layer_cou
   return EMM_OK;
 }
 
-}  // extern "C"
-
-template <typename V>
-static void launch_append_segments(emm_ctx *ctx, const emm::AppendArgs &a, cudaStream_t st) {
-  const uint32_t row_vecs = a.row_bytes / (uint32_t)sizeof(V);
-  const uint32_t segs_per_row = (row_vecs + 31u) / 32u;
-  const uint64_t rows = (uint64_t)a.layer_count * (uint64_t)a.num_tokens * 2ull;
-  const uint64_t total = rows * segs_per_row;
-  const int per_sm = ctx->append_ctas_per_sm > 0 ? ctx->append_ctas_per_sm : 8;
-  const uint64_t cap = (uint64_t)ctx->sm_count * per_sm;  // CTAs resident at once
-  int unroll = ctx->append_unroll;
-  if (unroll <= 0) {
-    // as few items per warp as keep the whole job in one resident wave
-    const uint64_t per_warp = (total + cap * emm::kAppendWarps - 1) / (cap * emm::kAppendWarps);
-    unroll = per_warp <= 1 ? 1 : per_warp <= 2 ? 2 : per_warp <= 4 ? 4 : 8;
-  }
-  const uint64_t want = (total + (uint64_t)emm::kAppendWarps * unroll - 1) / ((uint64_t)emm::kAppendWarps * unroll);
-  const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>(want, cap));
-  const int block = emm::kAppendWarps * 32;
-  switch (unroll) {
-    case 1: emm::append_segments<V, 1><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
-    case 2: emm::append_segments<V, 2><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
-    case 4: emm::append_segments<V, 4><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
-    default: emm::append_segments<V, 8><<<grid, block, 0, st>>>(a, segs_per_row, total); break;
-  }
-}
-
-extern "C" {
-
 // Launches the append kernel for prepared arguments. Call with the context's device current.
 static int append_launch(emm_ctx *ctx, const emm::AppendArgs &a, uint32_t align, cudaStream_t st) {
   if (a.num_tokens == 0 || a.layer_count == 0) return EMM_OK;
   const uint64_t rows = (uint64_t)a.layer_count * (uint64_t)a.num_tokens * 2ull;
-  if (ctx->append_variant == 2) {
-    if (align >= 16) launch_append_segments<uint4>(ctx, a, st);
-    else if (align >= 8) launch_append_segments<uint2>(ctx, a, st);
-    else if (align >= 4) launch_append_segments<uint32_t>(ctx, a, st);
-    else if (align >= 2) launch_append_segments<uint16_t>(ctx, a, st);
-    else launch_append_segments<uint8_t>(ctx, a, st);
-  } else {
-    const int grid = (int)((rows + emm::kAppendWarps - 1) / emm::kAppendWarps);
-    const int block = emm::kAppendWarps * 32;
-    if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
-    else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
-    else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
-    else if (align >= 2) emm::append_rows<uint16_t, 4><<<grid, block, 0, st>>>(a);
-    else emm::append_rows<uint8_t, 4><<<grid, block, 0, st>>>(a);
-  }
+  const int grid = (int)((rows + emm::kAppendWarps - 1) / emm::kAppendWarps);
+  const int block = emm::kAppendWarps * 32;
+  if (align >= 16) emm::append_rows<uint4, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 8) emm::append_rows<uint2, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 4) emm::append_rows<uint32_t, 4><<<grid, block, 0, st>>>(a);
+  else if (align >= 2) emm::append_rows<uint16_t, 4><<<grid, block, 0, st>>>(a);
+  else emm::append_rows<uint8_t, 4><<<grid, block, 0, st>>>(a);
   EMM_CUDA(cudaGetLastError());
   ctx->launches += 1;
   return EMM_OK;
@@ -1635,6 +1628,8 @@ int emm_gather_noalloc(int device, const emm_pool_desc *desc, const void *const 
   a.status = reinterpret_cast<int *>(d_status);
   a.wait_limit_ns = emm::kDefaultWaitLimitNs;
   a.tx_overcount = 0;
+  a.inline_count = 0;
+  a.src_inline = a.dst_inline = 0;
 
   if (align >= 16) {
     int64_t chunk = std::min<int64_t>(32768, page);

@@ -48,6 +48,8 @@ struct CopySide {
   uint64_t seg_stride;         // bytes one block occupies over the moved layers and planes
 };
 
+constexpr int kInlineIds = 64;  // longest table carried in the kernel arguments
+
 struct PageCopyArgs {
   CopySide src;
   CopySide dst;
@@ -60,6 +62,11 @@ struct PageCopyArgs {
   uint32_t chunks_per_page;  // ceil(page_bytes / chunk_bytes)
   uint64_t total_chunks;     // layer_count * planes * n * chunks_per_page
   int *status;               // [0] = sticky status code, [1..2] = detail (lo, hi)
+  // Short tables travel in the kernel arguments instead of device memory (no staging copy before the
+  // launch): when inline_count > 0, a side with use_inline set reads its ids from inline_ids[side].
+  uint32_t inline_count;
+  uint32_t src_inline, dst_inline;
+  int32_t inline_ids[2][kInlineIds];
   uint64_t wait_limit_ns;    // bulk family: longest a lane waits for one load before it gives up
   uint32_t tx_overcount;     // bulk family, test hook: bytes added to every expected transaction count
                              // (0 in every product path; non-zero makes each wait run out)
@@ -120,13 +127,12 @@ __device__ __forceinline__ ChunkAddr decode_chunk(const PageCopyArgs &a, uint64_
   uint32_t rem = a.page_bytes - off;
   r.len = rem < a.chunk_bytes ? rem : a.chunk_bytes;
 
-  int32_t sid = a.src.ids ? a.src.ids[i] : (int32_t)i;
-  int32_t did = a.dst.ids ? a.dst.ids[i] : (int32_t)i;
-  bool bad = (a.src.ids && (uint32_t)sid >= a.src.num_blocks) ||
-             (a.dst.ids && (uint32_t)did >= a.dst.num_blocks);
+  const bool s_tab = a.src.ids || a.src_inline, d_tab = a.dst.ids || a.dst_inline;
+  int32_t sid = a.src.ids ? a.src.ids[i] : (a.src_inline ? a.inline_ids[0][i] : (int32_t)i);
+  int32_t did = a.dst.ids ? a.dst.ids[i] : (a.dst_inline ? a.inline_ids[1][i] : (int32_t)i);
+  bool bad = (s_tab && (uint32_t)sid >= a.src.num_blocks) || (d_tab && (uint32_t)did >= a.dst.num_blocks);
   if (bad) {
-    report(a.status, kStatusIdRange,
-           (a.src.ids && (uint32_t)sid >= a.src.num_blocks) ? sid : did);
+    report(a.status, kStatusIdRange, (s_tab && (uint32_t)sid >= a.src.num_blocks) ? sid : did);
     r.len = 0;
     r.src = 0;
     r.dst = 0;
@@ -245,6 +251,17 @@ __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start
+// while its predecessor in the stream is still draining; it must not touch global memory before
+// grid_dependency_wait(), which returns once the predecessor has completed and its writes are visible.
+// Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -269,13 +286,14 @@ __device__ __forceinline__ void bulk_wait_all() {
 // decoded one iteration early so the table read is off the critical path.
 template <bool kSeg>
 __global__ void __launch_bounds__(kMaxWarps * 32)
-page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hint) {
+page_copy_bulk(const __grid_constant__ PageCopyArgs a, const uint32_t stages, const uint32_t l2_hint) {
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t bars[kMaxWarps * kMaxStages];
   __shared__ uint64_t slot_dst[kMaxWarps * kMaxStages];
   __shared__ uint32_t slot_len[kMaxWarps * kMaxStages];
 
   const uint32_t warp = threadIdx.x >> 5;
+  grid_launch_dependents();  // the next copy in the stream may set up while this one runs
   if ((threadIdx.x & 31) != 0) return;  // one issuing lane per warp
   const uint32_t warps = blockDim.x >> 5;
 
@@ -293,6 +311,7 @@ page_copy_bulk(const PageCopyArgs a, const uint32_t stages, const uint32_t l2_hi
   const uint64_t stream_step = (uint64_t)gridDim.x * warps;
   if (stream_id >= a.total_chunks) return;
   const uint64_t n_mine = (a.total_chunks - stream_id + stream_step - 1) / stream_step;
+  grid_dependency_wait();  // everything below reads or writes global memory
 
   // Issues the load of this stream's chunk into ring slot s.
   auto issue = [&](const ChunkAddr &ca, uint32_t s) {
@@ -394,7 +413,9 @@ __device__ __forceinline__ void store_stream<uint4>(uint4 *p, const uint4 &v) {
 // One CTA per chunk, grid-stride. Each thread moves up to U vectors of type V
 // per pass; all U loads are issued before the first store.
 template <typename V, int U, bool kSeg>
-__global__ void __launch_bounds__(256) page_copy_ldg(const PageCopyArgs a) {
+__global__ void __launch_bounds__(256) page_copy_ldg(const __grid_constant__ PageCopyArgs a) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   for (uint64_t g = blockIdx.x; g < a.total_chunks; g += gridDim.x) {
     const ChunkAddr ca = decode_chunk<kSeg>(a, g);
     if (ca.len == 0) continue;

@@ -245,7 +245,7 @@ class V0KVTransferManager:
             return True  # queued; moved by a later call or by flush()
         start = time.perf_counter()
         try:
-            res = self._run(src_rank, dst_rank, list(src_blocks), list(dst_blocks))
+            res = self._run(src_rank, dst_rank, src_blocks, dst_blocks)
         except Exception as e:
             res = {"error": f"{type(e).__name__}: {e}", "bytes": 0, "blocks": 0}
         elapsed = time.perf_counter() - start

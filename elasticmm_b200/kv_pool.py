@@ -16,6 +16,7 @@ and a single 6-D tensor [L, 2, NB, BS, H, D]
 from __future__ import annotations
 
 import ctypes as C
+import functools
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -338,7 +339,7 @@ class KVPool:
         """
         lc = self.num_layers - layer_begin if layer_count is None else layer_count
         lib = self.ctx._lib
-        st = C.c_void_p(_stream_ptr(self.device))
+        st = _stream_ptr(self.device)
         if isinstance(ids, torch.Tensor) and ids.is_cuda:
             self._check_table(ids, self.device)
             n = ids.numel()
@@ -353,7 +354,9 @@ class KVPool:
             return self.gather(self.upload_ids(self._validated(host)), out, layer_begin, lc)
         out = self.new_packed(n, lc) if out is None else out
         ptr, nbytes = self._packed_ptr(out, n, lc)
-        _lib.check(lib.emm_gather_h(self._h, host.ctypes.data_as(C.c_void_p), n, C.c_void_p(ptr), nbytes, st))
+        rc = lib.emm_gather_h(self._h, host.ctypes.data, n, ptr, nbytes, st)
+        if rc:
+            _lib.check(rc)
         return out
 
     def scatter(self, ids: IdList, packed: torch.Tensor,
@@ -361,7 +364,7 @@ class KVPool:
         """pool[l][p, ids[i]] = packed[l, p, i]; one launch for all layers."""
         lc = self.num_layers - layer_begin if layer_count is None else layer_count
         lib = self.ctx._lib
-        st = C.c_void_p(_stream_ptr(self.device))
+        st = _stream_ptr(self.device)
         if isinstance(ids, torch.Tensor) and ids.is_cuda:
             self._check_table(ids, self.device)
             n = ids.numel()
@@ -375,7 +378,9 @@ class KVPool:
             host = self._validated(host, unique=True)
             return self.scatter(self.upload_ids(host), packed, layer_begin, lc)
         ptr, nbytes = self._packed_ptr(packed, n, lc)
-        _lib.check(lib.emm_scatter_h(self._h, host.ctypes.data_as(C.c_void_p), n, C.c_void_p(ptr), nbytes, st))
+        rc = lib.emm_scatter_h(self._h, host.ctypes.data, n, ptr, nbytes, st)
+        if rc:
+            _lib.check(rc)
 
     # -- several requests per launch ---------------------------------------------------
     def _many_tables(self, id_lists: Sequence[IdList], unique: bool):
@@ -514,7 +519,7 @@ class KVPool:
             finally:
                 self.ctx.set_option(_lib.OPT_MAX_CTAS, before)
         lib = self.ctx._lib
-        st = C.c_void_p(_stream_ptr(self.device))
+        st = _stream_ptr(self.device)
         dev_tables = isinstance(src_ids, torch.Tensor) and src_ids.is_cuda
         if dev_tables != (isinstance(dst_ids, torch.Tensor) and dst_ids.is_cuda):
             raise ValueError("src_ids and dst_ids must both be host lists or both device tensors")
@@ -529,8 +534,9 @@ class KVPool:
         hs, hd = _as_host_ids(src_ids), _as_host_ids(dst_ids)
         if hs.shape != hd.shape:
             raise _lib.EmmError(_lib.ERR_LENGTH, "src_ids and dst_ids differ in length")
-        _lib.check(lib.emm_copy_blocks_h(self._h, dst._h, hs.ctypes.data_as(C.c_void_p),
-                                         hd.ctypes.data_as(C.c_void_p), hs.shape[0], st))
+        rc = lib.emm_copy_blocks_h(self._h, dst._h, hs.ctypes.data, hd.ctypes.data, hs.shape[0], st)
+        if rc:
+            _lib.check(rc)
 
     # -- staged transport over a library-owned or host-owned ncclComm_t --------------
     def send_blocks(self, comm: int, peer: int, ids: torch.Tensor, staging: torch.Tensor,
@@ -621,6 +627,8 @@ class KVPool:
 
         append.buffers = (key, value, slot_mapping, self)  # the closure keeps the buffers and the pool alive
         append.release = lambda: lib.emm_append_unbind(h)
+        # the bare foreign call for hot loops: raw(layer, stream) returns the status code (0 = ok)
+        append.raw = functools.partial(fn, h)
         return append
 
     def append_all_layers(self, key: torch.Tensor, value: torch.Tensor,

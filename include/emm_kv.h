@@ -93,9 +93,8 @@ enum emm_option {
   EMM_OPT_MAX_CTAS = 6,      /* cap on the grid (0 = none) */
   EMM_OPT_REMOTE_VARIANT = 7, /* family used when a side is a peer GPU's or pinned host memory (default LDG) */
   EMM_OPT_L2_HINT = 8,        /* bulk variant: bit 0 loads, bit 1 stores carry an L2 evict-first hint (default 0) */
-  EMM_OPT_APPEND_VARIANT = 10,     /* append kernel: 0 automatic, 1 one warp per row, 2 segment-granular grid */
-  EMM_OPT_APPEND_UNROLL = 11,      /* segment-granular append: 16-byte accesses in flight per lane (0 = automatic) */
-  EMM_OPT_APPEND_CTAS_PER_SM = 12, /* segment-granular append: resident CTAs per SM the grid is capped at (0 = 8) */
+  EMM_OPT_PDL = 10,                /* bulk variant: launch with programmatic stream serialisation, so that a copy
+                                      sets up while the previous copy in the stream drains (default 1) */
   EMM_OPT_WAIT_LIMIT_NS = 9   /* bulk variant: longest one device-side wait for a load may last, in ns
                                  (default 2 s, range 1 us .. 60 s); when it runs out the kernel records
                                  EMM_ERR_TIMEOUT in the status word, drains and returns */

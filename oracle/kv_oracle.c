@@ -10,7 +10,7 @@
  *   kvo_scatter       V0Worker.write_kv_blocks    elasticmm/engine/v0/worker.py:612-633
  *   kvo_copy_blocks   gather followed by scatter; per-block copy of V0Worker.swap_blocks
  *                                                 elasticmm/engine/v0/worker.py:520-526
- *   kvo_append        the cache op under execute_model (vLLM; parity unpinned)
+ *   kvo_append        the cache op under execute_model (vLLM; checked against a fixture its op produced)
  *                                                 elasticmm/engine/v0/worker_steps.py:281,438
  *   kvo_compact_plan  no reference counterpart; the free list it repairs is
  *                                                 elasticmm/engine/v0/block_manager.py:247-256

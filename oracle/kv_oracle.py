@@ -14,11 +14,19 @@ Parity status
   * 6-D single-tensor transfer and GPU<->CPU swap: restated from the source
     (the reference functions need a process group / CUDA streams and cannot
     run on CPU); pinned indirectly, because they must equal gather->scatter.
-  * append (reshape_and_cache): PARITY UNPINNED. The arithmetic lives in vLLM
-    (requirement `vllm>=0.10.1`, V0 model runner), which is not part of the
-    reference tree and whose V0 worker API is absent from the installed vLLM.
-    The restatement follows the published semantics: slot s -> block s // BS,
-    offset s % BS; negative slots are padding.
+  * append (reshape_and_cache): PINNED against the third-party op the
+    reference runs. The arithmetic lives in vLLM (requirement `vllm>=0.10.1`),
+    which is not part of the reference tree; the reference reaches it under
+    model_runner.execute_model (elasticmm/engine/v0/worker_steps.py:281,438).
+    vLLM's reshape_and_cache_flash (the op for the [2, NB, BS, H, D] pool the
+    reference binds, elasticmm/engine/v0/worker.py:380-412) was run on a B200
+    (vLLM 0.22.0) by tests/golden/make_append_golden.py on the seeded inputs of
+    tests/golden/cases.py; its output pools are the fixture
+    tests/golden/append_golden.npz, which tests/test_oracle_golden.py checks
+    this restatement against (slot s -> block s // BS, offset s % BS; negative
+    slots are padding). Head rows that are not multiples of 16 bytes are outside
+    what vLLM's kernel accepts (it raised "misaligned address" on 10-byte rows)
+    and stay restatement-only.
   * compaction: no reference implementation exists; defined as
     extract_kv_blocks(old ids) followed by write_kv_blocks(new ids).
 
@@ -122,7 +130,7 @@ def transfer_vision_blocks(src_cache: torch.Tensor, dst_cache: torch.Tensor, src
 
 
 # ---------------------------------------------------------------------------
-# append (parity unpinned, see the module docstring)
+# append (pinned against vLLM's op through tests/golden/append_golden.npz, see the module docstring)
 # ---------------------------------------------------------------------------
 
 def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, layer_kv: torch.Tensor,
