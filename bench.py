@@ -806,8 +806,8 @@ NVLINK_NOMINAL_GBS = 900.0  # NVLink 5, per direction per GPU
 def build_wave_plans(w, sources, sinks, seed=4):
     """Splits the workload's requests over the sources, assigns each a seeded sink, and packs them into waves.
 
-    A wave may occupy half of every pool (source and sink blocks of wave k are reused by wave k + 2, so two
-    waves can be in flight). Within a wave a source fills its half so that its sinks receive about the same
+    When everything fits the pools at once there is a single wave. Otherwise a wave may occupy half of every
+    pool (source and sink blocks of wave k are reused by wave k + 2, so two waves can be in flight). Within a wave a source fills its half so that its sinks receive about the same
     number of blocks: it repeatedly gives the sink that has the least so far the largest remaining request
     that still fits. Block tables are seeded permutations of the half the wave may use."""
     from elasticmm_b200.engine.v0 import MigrationPlan, Transfer
@@ -815,13 +815,16 @@ def build_wave_plans(w, sources, sinks, seed=4):
     counts = request_blocks(w, seed)
     g = torch.Generator().manual_seed(seed)
     assign = torch.randint(0, len(sinks), (len(counts),), generator=g).tolist()
-    half = w["NB"] // 2
+    per_source = [sum(c for i, c in enumerate(counts) if i % len(sources) == k) for k in range(len(sources))]
+    per_sink = [sum(c for i, c in enumerate(counts) if assign[i] == j) for j in range(len(sinks))]
+    one_wave = max(per_source) <= w["NB"] and max(per_sink) <= w["NB"]  # everything fits the pools at once
+    half = w["NB"] if one_wave else w["NB"] // 2
     remaining = {s: {d: sorted((i for i in range(len(counts)) if i % len(sources) == k and sinks[assign[i]] == d),
                                key=lambda i: -counts[i]) for d in sinks} for k, s in enumerate(sources)}
     plans, wv = [], 0
     carry = {s: {d: 0.0 for d in sinks} for s in sources}  # blocks a sink is behind (+) or ahead (-) of its fair share
     while any(lst for per in remaining.values() for lst in per.values()):
-        base = (wv % 2) * half
+        base = 0 if one_wave else (wv % 2) * half
         plan = MigrationPlan()
         sink_used = {d: 0 for d in sinks}
         sink_perm = {d: (torch.randperm(half, generator=torch.Generator().manual_seed(77 * wv + d)) + base).tolist()
@@ -1037,20 +1040,32 @@ def bench_multi(args):
 
     # ---- reference rates measured in this run --------------------------------------------------------------
     probe = {}
-    if worker._nccl_comm is not None and rank in (sources[0], sinks[0]):
-        pass  # measured below by both ends
     one_gib = torch.empty(1 << 30, dtype=torch.uint8, device=device)
-
-    def nccl_pair():
-        if rank == sources[0]:
-            worker.ctx.send_packed(worker._nccl_comm, one_gib, sinks[0])
-        elif rank == sinks[0]:
-            worker.ctx.recv_packed(worker._nccl_comm, one_gib, sources[0])
-
+    two_gib = torch.empty(1 << 30, dtype=torch.uint8, device=device)
     if worker._nccl_comm is not None:
-        ms_p = max_ms(timed(nccl_pair, 5, 2, device, barrier))
-        probe["nccl_sendrecv_1gib_gbs"] = round((1 << 30) * 5 / (ms_p / 1e3) / 1e9, 1)
-    del one_gib
+        # raw ncclSend/ncclRecv between the first source and the first sink, no pack or unpack: the library's ceiling
+        table = {}
+        for mib in (64, 256, 1024):
+            n = mib << 20
+
+            def nccl_pair():
+                if rank == sources[0]:
+                    worker.ctx.send_packed(worker._nccl_comm, one_gib[:n], sinks[0])
+                elif rank == sinks[0]:
+                    worker.ctx.recv_packed(worker._nccl_comm, one_gib[:n], sources[0])
+
+            def nccl_both():
+                if rank in (sources[0], sinks[0]):
+                    other = sinks[0] if rank == sources[0] else sources[0]
+                    worker.ctx.exchange(worker._nccl_comm, [(True, one_gib[:n], other), (False, two_gib[:n], other)])
+
+            ms_p = max_ms(timed(nccl_pair, 5, 2, device, barrier))
+            ms_b = max_ms(timed(nccl_both, 5, 2, device, barrier))
+            table[f"{mib}MiB"] = {"one_way": round(n * 5 / (ms_p / 1e3) / 1e9, 1),
+                                  "both_ways_per_direction": round(n * 5 / (ms_b / 1e3) / 1e9, 1)}
+        probe["nccl_sendrecv_gbs"] = table
+        probe["nccl_sendrecv_1gib_gbs"] = table["1024MiB"]["one_way"]
+    del one_gib, two_gib
     # one contiguous flow through the copy kernel: the first sink loads the first quarter of the first source's pool
     quarter = w["NB"] // 4
     flow_ids = worker.pool.upload_ids(list(range(quarter)))

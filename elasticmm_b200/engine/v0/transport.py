@@ -23,7 +23,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 Chunk = Tuple[int, int]  # (layer_begin, layer_count)
 
-DEFAULT_MESSAGE_BYTES = 64 << 20
+DEFAULT_MESSAGE_BYTES = 512 << 20  # NCCL reaches its upper point-to-point rate from about half a gibibyte per message
 PIPELINE_DEPTH = 2
 
 
@@ -289,13 +289,14 @@ class WaveLedger:
                                    f"sinks finished within {self.timeout_s} s")
             if pause:
                 time.sleep(pause)
-                pause = min(pause * 2, 500e-6)  # a long wait polls the store gently
+                pause = min(pause * 2, 200e-6)  # a long wait polls the store gently
 
 
 def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, depth: int,
               launch: Callable[[int, int, List[object]], object],
               wait_done: Callable[[object], float],
-              on_wave_landed: Optional[Callable[[int], None]] = None) -> List[float]:
+              on_wave_landed: Optional[Callable[[int], None]] = None,
+              wait_for_readers: bool = True) -> List[float]:
     """Drives one rank through a sequence of waves without a barrier between waves.
 
     Sink side. For wave w and each of its sources (in the plan's pull order):
@@ -311,7 +312,9 @@ def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, d
     source with it; depth 1 degenerates to one wave at a time.
 
     Source side. A source returns once every one of its waves is complete
-    everywhere: from then on all the blocks it offered may be freed.
+    everywhere: from then on all the blocks it offered may be freed. A caller
+    that ends the migration with a meeting of all ranks anyway passes
+    wait_for_readers=False and lets that meeting carry the same guarantee.
 
     Returns this rank's per-wave durations (the longest copy of each wave; empty
     for a rank that receives nothing).
@@ -347,8 +350,9 @@ def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, d
     while finished < len(plans):
         finish(finished)
         finished += 1
-    for w, plan in enumerate(plans):
-        n = len(plan.outgoing(rank))
-        if n:
-            ledger.wait(w, rank, n)
+    if wait_for_readers:
+        for w, plan in enumerate(plans):
+            n = len(plan.outgoing(rank))
+            if n:
+                ledger.wait(w, rank, n)
     return wave_ms

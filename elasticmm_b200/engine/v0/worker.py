@@ -25,7 +25,13 @@ from ...kv_pool import Context, KVPool, _as_host_ids, get_context
 from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_recv,
                         pipelined_send, run_waves, PIPELINE_DEPTH)
 
-ALLTOALL_MESSAGE_BYTES = 256 << 20  # target bytes a rank packs per chunk of the all-to-all migration
+# All-to-all migration. A rank packs about this many bytes per chunk of layers: NCCL moves one message of up
+# to 256 MiB at ~550 GB/s and messages of 512 MiB and more at ~690 GB/s (measured between two B200s), so the
+# chunks are large. The pack and unpack kernels are capped to the SM count minus this many CTAs: an NCCL
+# point-to-point CTA needs an SM almost to itself, and with all 148 SMs held by a copy kernel the exchange that
+# runs beside it fell from ~630 to ~565 GB/s.
+ALLTOALL_MESSAGE_BYTES = 1 << 30
+ALLTOALL_SMS_LEFT_TO_NCCL = 48
 from .utils import EngineStage
 
 import contextlib
@@ -581,6 +587,34 @@ class V0Worker:
             return None
         return error or "another rank of the migration reported an error; nothing was moved by this rank"
 
+    def _post_flag(self, error: Optional[str]):
+        """The non-blocking half of an agreement: starts the all-reduce of this rank's error flag on the
+        current stream and returns the tensor; _read_flags turns one or more of them into a verdict. On a
+        GPU group nothing here waits for the device, so kernels queued behind the all-reduce are ordered
+        after every rank's arrival without the host stalling."""
+        backend = dist.get_backend(self.process_group)
+        flag = torch.tensor([1 if error else 0], dtype=torch.int32,
+                            device=self.device if backend == "nccl" else "cpu")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.process_group)
+        return flag
+
+    @staticmethod
+    def _read_flags(flags, error: Optional[str]) -> Optional[str]:
+        if not any(int(f.item()) for f in flags):
+            return None
+        return error or "another rank of the migration reported an error; this rank's part may have run"
+
+    def _plan_error(self, plan: MigrationPlan, method: str) -> Optional[str]:
+        """_check_plan_part, remembered per plan: a plan that is replayed (the waves of a long migration,
+        a benchmark step) is validated on the host once."""
+        key = (id(plan), len(plan.transfers), method, tuple(sorted(self.peer_pools)))
+        cache = self.__dict__.setdefault("_plan_checks", {})
+        if key not in cache:
+            if len(cache) > 256:
+                cache.clear()
+            cache[key] = (plan, self._check_plan_part(plan, method))  # the plan is kept so that its id stays unique
+        return cache[key][1]
+
     def _own_stream_sync(self) -> None:
         torch.cuda.current_stream(self.device).synchronize()
 
@@ -678,7 +712,7 @@ class V0Worker:
         if method not in ("pull", "push", "alltoall", "nccl"):
             raise ValueError(f"unknown migration method {method!r}")
         rank = self.get_global_rank()
-        error = self._check_plan_part(plan, method)
+        error = self._plan_error(plan, method)
         if plan.outgoing(rank):
             self._own_stream_sync()  # what this source wrote is visible to its sinks
         error = self._agree(error)
@@ -742,18 +776,22 @@ class V0Worker:
         finished and before it posts the wave (a verification hook).
 
         Returns {"bytes", "blocks", "wave_ms"} with this sink's device time per wave,
-        or {"error": ...} on every rank if any rank failed.
+        or {"error": ...} on every rank if any rank failed (a rank that failed its
+        host-side checks moves nothing; the others may have moved their part).
         """
         rank = self.get_global_rank()
         pool = self.pool
         error = None
         for plan in plans:
-            error = error or self._check_plan_part(plan, "pull")
+            error = error or self._plan_error(plan, "pull")
         if any(plan.outgoing(rank) for plan in plans):
             self._own_stream_sync()
-        error = self._agree(error)
+        # Entry agreement without a host stall: the flag's all-reduce sits on the current stream, the pulls
+        # are ordered behind it, and its value is read together with the exit flag.
+        entry = self._post_flag(error)
         if error:
-            return {"error": error, "bytes": 0, "blocks": 0}
+            exit_flag = self._post_flag(error)
+            return {"error": self._read_flags([entry, exit_flag], error), "bytes": 0, "blocks": 0}
         moved, wave_ms = [0], []
         try:
             def launch(w: int, peer: int, earlier):
@@ -763,7 +801,7 @@ class V0Worker:
                 stream = self._peer_streams.get(peer)
                 if stream is None:
                     stream = self._peer_streams[peer] = torch.cuda.Stream(self.device)
-                if w == 0:
+                if w < depth:  # behind the entry agreement (later waves follow their predecessors on this stream)
                     stream.wait_stream(torch.cuda.current_stream(self.device))
                 for _, done in earlier:  # this sink's copies of wave w - depth, from any source, are done
                     stream.wait_event(done)
@@ -781,7 +819,8 @@ class V0Worker:
                 handle[1].synchronize()
                 return handle[0].elapsed_time(handle[1])
 
-            wave_ms = run_waves(plans, rank, ledger, depth, launch, wait_done, on_wave_landed)
+            wave_ms = run_waves(plans, rank, ledger, depth, launch, wait_done, on_wave_landed,
+                                wait_for_readers=False)  # the exit agreement below tells a source the same
             main = torch.cuda.current_stream(self.device)
             for stream in self._peer_streams.values():
                 main.wait_stream(stream)
@@ -793,7 +832,7 @@ class V0Worker:
                 pass
         if not error:
             error = self._device_error("pull")
-        error = self._agree(error)
+        error = self._read_flags([entry, self._post_flag(error)], error)
         if error:
             return {"error": error, "bytes": 0, "blocks": 0}
         return {"bytes": moved[0] * pool.block_bytes(), "blocks": moved[0], "wave_ms": wave_ms}
@@ -824,12 +863,18 @@ class V0Worker:
             totals[("o", t.src_rank)] = totals.get(("o", t.src_rank), 0) + len(t.src_blocks)
             totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
         n_ref = max(totals.values()) if totals else 0
-        chunks = plan_chunks(pool.num_layers, n_ref, page, target_bytes=ALLTOALL_MESSAGE_BYTES)
+        chunks = plan_chunks(pool.num_layers, n_ref, page,
+                             target_bytes=getattr(self, "alltoall_chunk_bytes", ALLTOALL_MESSAGE_BYTES))
         if not chunks:
             return 0
         lc_max = max_chunk_layers(chunks)
 
         ctx = self.ctx
+        # pack and unpack leave some SMs to the NCCL kernel that runs beside them
+        copy_ctas = getattr(self, "alltoall_copy_ctas", max(16, ctx.sm_count - ALLTOALL_SMS_LEFT_TO_NCCL))
+        saved_cap = ctx.get_option(_lib.OPT_MAX_CTAS)
+        if copy_ctas:
+            ctx.set_option(_lib.OPT_MAX_CTAS, copy_ctas)
         main = torch.cuda.current_stream(self.device)
         if self._a2a is None:
             self._a2a = {"pack": torch.cuda.Stream(self.device), "wire": torch.cuda.Stream(self.device),
@@ -888,4 +933,5 @@ class V0Worker:
                         ev_unpacked[slot].record(a2a["unpack"])
         for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
             main.wait_stream(st)
+        ctx.set_option(_lib.OPT_MAX_CTAS, saved_cap)
         return N_out + N_in
