@@ -966,6 +966,7 @@ def bench_multi(args):
             if t.src_rank == rank:
                 idx = torch.tensor(t.src_blocks, dtype=torch.long, device=device)
                 dist.send(torch.stack([layer[:, idx] for layer in kv], dim=0), dst=t.dst_rank)
+                torch.cuda.current_stream(device).synchronize()  # one request's copy in flight at a time
             elif t.dst_rank == rank:
                 idx = torch.tensor(t.dst_blocks, dtype=torch.long, device=device)
                 got = torch.stack([layer[:, idx] for layer in kv], dim=0)

@@ -505,3 +505,19 @@ def test_one_process_two_gpus(direction):
             assert mgr.transfer_kv_cache_sync(rid, 0, 1, s, d), mgr.last_result
             kv_oracle.write_kv_blocks(dst_cpu, d, kv_oracle.extract_kv_blocks(src_cpu, s))
         assert all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(dst.kv_cache, dst_cpu)), method
+        if method == TransferMethod.B200_PEER:
+            # The source pool is rewritten by work still queued on the source GPU's stream when the transfer
+            # is requested: the sink's kernel must be ordered after it (no synchronisation in between).
+            new_cpu = kv_oracle.make_pool(geom["L"], geom["NB"], geom["BS"], geom["H"], geom["D"], torch.bfloat16, 6)
+            staged = [t.to("cuda:0") for t in new_cpu]
+            busy = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+            torch.cuda.synchronize()
+            with torch.cuda.device("cuda:0"):
+                for _ in range(20):
+                    busy.add_(1)                              # keeps the source stream busy for a while
+                for layer, new in zip(src.kv_cache, staged):
+                    layer.copy_(new, non_blocking=True)       # the "prefill" that produces the blocks
+            rid, s, d = reqs[0]
+            assert mgr.transfer_kv_cache_sync("late", 0, 1, s, d), mgr.last_result
+            kv_oracle.write_kv_blocks(dst_cpu, d, kv_oracle.extract_kv_blocks(new_cpu, s))
+            assert all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(dst.kv_cache, dst_cpu)), "pull not ordered"
