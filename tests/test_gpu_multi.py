@@ -379,6 +379,91 @@ def test_two_ranks_sharing_one_gpu_pull_migration_is_bit_exact():
             assert v is True, f"{k} failed: {r}"
 
 
+def _one_gpu_four_ranks_main(rank, world, port, out_dir):
+    """Four processes on cuda:0: ranks 0, 1 are sources, ranks 2, 3 sinks (the 2 -> 2 rebalancing pattern).
+    Every sink pulls from both sources side by side with capped grids, in three waves two deep; then one plan
+    through the manager. gloo carries the agreement, CUDA IPC the pools."""
+    import torch.distributed as dist
+
+    from elasticmm_b200.engine.v0 import MigrationPlan, TransferMethod, V0KVTransferManager, V0Worker
+    from elasticmm_b200.engine.v0.transport import WaveLedger
+    from oracle import kv_oracle
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    geom = dict(GEOM, L=6, NB=256)
+    is_src = rank < 2
+
+    def pool_cpu(r):
+        return kv_oracle.make_pool(geom["L"], geom["NB"], geom["BS"], geom["H"], geom["D"], torch.bfloat16,
+                                   80 + r if r < 2 else 0, fill="normal" if r < 2 else "guard")
+
+    def fresh():
+        w = V0Worker(worker_id=rank, dtype="bfloat16", device=dev, global_rank=rank, world_size=world,
+                     kv_cache=[t.to(dev) for t in pool_cpu(rank)])
+        w.init_global_nccl()
+        hs = [None] * world
+        dist.all_gather_object(hs, (w.get_ipc_handles(), w.get_pool_desc()))
+        for peer in range(world):
+            if peer != rank:
+                w.attach_peer_pool(peer, hs[peer][0], hs[peer][1])
+        return w
+
+    g = torch.Generator().manual_seed(17)
+    plan = MigrationPlan()
+    used = {2: 0, 3: 0}
+    dperm = {d: torch.randperm(geom["NB"], generator=g).tolist() for d in (2, 3)}
+    for s in (0, 1):
+        sperm = torch.randperm(geom["NB"], generator=g).tolist()
+        pos = 0
+        for r in range(9):
+            n = int(torch.randint(3, 25, (1,), generator=g))
+            d = 2 + int(torch.randint(0, 2, (1,), generator=g))
+            from elasticmm_b200.engine.v0 import Transfer
+            plan.add(Transfer(f"s{s}r{r}", s, d, tuple(sperm[pos:pos + n]), tuple(dperm[d][used[d]:used[d] + n])))
+            pos += n
+            used[d] += n
+    plan.validate(lambda r: geom["NB"])
+
+    def expected():
+        want = pool_cpu(rank)
+        for s in plan.incoming(rank):
+            si, di = plan.tables(s, rank)
+            kv_oracle.write_kv_blocks(want, di, kv_oracle.extract_kv_blocks(pool_cpu(s), si))
+        return want
+
+    results = {}
+    w = fresh()
+    waves = [MigrationPlan(plan.transfers[k::3]) for k in range(3)]
+    res = w.migrate_waves(waves, WaveLedger(dist.distributed_c10d._get_default_store(), "test1x4/waves"), depth=2)
+    results["waves_ok"] = "error" not in res and (is_src or len(res["wave_ms"]) == 3)
+    if not is_src:
+        results["waves_exact"] = all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, expected()))
+    dist.barrier()
+    w = fresh()
+    mgr = V0KVTransferManager(transfer_method=TransferMethod.B200_PEER)
+    mgr.register_worker(rank, w, "prefill" if is_src else "decoding")
+    launches = w.ctx.launch_count
+    results["plan_ok"] = mgr.transfer_many(plan) and (w.ctx.launch_count - launches) == (0 if is_src else 2)
+    if not is_src:
+        results["plan_exact"] = all(kv_oracle.bit_equal(a.cpu(), b) for a, b in zip(w.kv_cache, expected()))
+    dist.barrier()
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_four_ranks_sharing_one_gpu_two_sources_two_sinks_is_bit_exact():
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_one_gpu_four_ranks_main, args=(4, _free_port(), d), nprocs=4, join=True)
+        for r in range(4):
+            res = torch.load(os.path.join(d, f"r{r}.pt"))
+            assert len(res) == (2 if r < 2 else 4) and all(v is True for v in res.values()), f"rank {r}: {res}"
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_gpu_migration_is_bit_exact():
     import torch.multiprocessing as mp
