@@ -14,6 +14,8 @@ rather than raised, precondition failures raise ValueError / RuntimeError
 """
 from __future__ import annotations
 
+import contextlib
+import os
 import time
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -33,9 +35,6 @@ from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_
 ALLTOALL_MESSAGE_BYTES = 1 << 30
 ALLTOALL_SMS_LEFT_TO_NCCL = 48
 from .utils import EngineStage
-
-import contextlib
-import os
 
 _NVTX = os.environ.get("EMM_NVTX", "0") == "1"
 

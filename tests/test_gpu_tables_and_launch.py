@@ -4,7 +4,6 @@ Host lists of up to 64 ids travel in the kernel arguments, longer ones through t
 ring; tables kept on the device are uploaded once with emm_upload_ids; several peers' blocks are
 packed per peer for a layer range (the packed side of an all-to-all). Every form must give what
 the reference's extract_kv_blocks / write_kv_blocks give (elasticmm/engine/v0/worker.py:578-633)."""
-import ctypes as C
 
 import numpy as np
 import pytest
