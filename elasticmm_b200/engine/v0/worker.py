@@ -26,6 +26,7 @@ from ... import _lib
 from ...kv_pool import Context, KVPool, _as_host_ids, get_context
 from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_recv,
                         pipelined_send, run_waves, PIPELINE_DEPTH)
+from .utils import EngineStage
 
 # All-to-all migration. A rank packs about this many bytes per chunk of layers: NCCL moves one message of up
 # to 256 MiB at ~550 GB/s and messages of 512 MiB and more at ~690 GB/s (measured between two B200s), so the
@@ -34,7 +35,6 @@ from .transport import (MigrationPlan, plan_chunks, max_chunk_layers, pipelined_
 # runs beside it fell from ~630 to ~565 GB/s.
 ALLTOALL_MESSAGE_BYTES = 1 << 30
 ALLTOALL_SMS_LEFT_TO_NCCL = 48
-from .utils import EngineStage
 
 _NVTX = os.environ.get("EMM_NVTX", "0") == "1"
 
