@@ -331,8 +331,9 @@ def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, d
             longest = max(longest, float(wait_done(handle)))
         if on_wave_landed is not None:
             on_wave_landed(w)
-        for source, _ in launched[w]:
-            ledger.post(w, source)
+        if wait_for_readers or w + depth < len(plans):  # nobody reads the record of the last waves otherwise
+            for source, _ in launched[w]:
+                ledger.post(w, source)
         if launched[w]:
             wave_ms.append(longest)
 
