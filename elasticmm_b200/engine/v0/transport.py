@@ -316,14 +316,15 @@ def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, d
     that ends the migration with a meeting of all ranks anyway passes
     wait_for_readers=False and lets that meeting carry the same guarantee.
 
-    Returns this rank's per-wave durations (the longest copy of each wave; empty
-    for a rank that receives nothing).
+    Returns this rank's per-wave durations (the longest copy of each wave, one
+    entry per wave; empty for a rank that receives nothing in any wave).
     """
     if depth < 1:
         raise ValueError("depth must be at least 1")
     launched: List[List[Tuple[int, object]]] = []
     wave_ms: List[float] = []
     finished = 0  # waves [0, finished) of this rank are complete and posted
+    is_sink = any(plan.incoming(rank) for plan in plans)
 
     def finish(w: int) -> None:
         longest = 0.0
@@ -334,8 +335,8 @@ def run_waves(plans: Sequence["MigrationPlan"], rank: int, ledger: WaveLedger, d
         if wait_for_readers or w + depth < len(plans):  # nobody reads the record of the last waves otherwise
             for source, _ in launched[w]:
                 ledger.post(w, source)
-        if launched[w]:
-            wave_ms.append(longest)
+        if is_sink:
+            wave_ms.append(longest)  # 0.0 for a wave in which this sink receives nothing
 
     for w, plan in enumerate(plans):
         this_wave: List[Tuple[int, object]] = []
