@@ -28,11 +28,14 @@ PIPELINE_DEPTH = 2
 
 
 def plan_chunks(num_layers: int, n_blocks: int, page_bytes: int,
-                target_bytes: int = DEFAULT_MESSAGE_BYTES) -> List[Chunk]:
+                target_bytes: int = DEFAULT_MESSAGE_BYTES, taper: bool = False) -> List[Chunk]:
     """Splits the L layers into consecutive chunks of about `target_bytes` each.
 
     One layer of n blocks is 2*n*page_bytes on the wire. At least two chunks
-    are produced whenever L >= 2 so that packing and sending can overlap.
+    are produced whenever L >= 2 so that packing and sending can overlap. With
+    `taper` the first and the last chunk are a single layer: the first chunk's
+    pack and the last chunk's unpack are the only parts of a pipelined transfer
+    that nothing overlaps, so they should be short.
     """
     if num_layers <= 0 or n_blocks <= 0:
         return []
@@ -40,6 +43,9 @@ def plan_chunks(num_layers: int, n_blocks: int, page_bytes: int,
     per_chunk = max(1, min(num_layers, target_bytes // max(1, layer_bytes)))
     if num_layers >= 2:
         per_chunk = min(per_chunk, (num_layers + 1) // 2)
+    if taper and per_chunk > 1 and num_layers >= 3:
+        inner = [(1 + b, min(per_chunk, num_layers - 2 - b)) for b in range(0, num_layers - 2, per_chunk)]
+        return [(0, 1)] + inner + [(num_layers - 1, 1)]
     return [(b, min(per_chunk, num_layers - b)) for b in range(0, num_layers, per_chunk)]
 
 

@@ -863,7 +863,7 @@ class V0Worker:
             totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
         n_ref = max(totals.values()) if totals else 0
         chunks = plan_chunks(pool.num_layers, n_ref, page,
-                             target_bytes=getattr(self, "alltoall_chunk_bytes", ALLTOALL_MESSAGE_BYTES))
+                             target_bytes=getattr(self, "alltoall_chunk_bytes", ALLTOALL_MESSAGE_BYTES), taper=True)
         if not chunks:
             return 0
         lc_max = max_chunk_layers(chunks)

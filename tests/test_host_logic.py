@@ -190,6 +190,11 @@ def test_chunk_schedule():
         assert ch[0][0] == 0 and sum(c for _, c in ch) == L
         assert all(a[0] + a[1] == b[0] for a, b in zip(ch, ch[1:]))
         assert len(ch) >= 2
+        tp = plan_chunks(L, n, page, target_bytes=1 << 30, taper=True)      # short first and last chunk
+        assert tp[0][0] == 0 and sum(c for _, c in tp) == L and all(c > 0 for _, c in tp)
+        assert all(a[0] + a[1] == b[0] for a, b in zip(tp, tp[1:]))
+        if max(c for _, c in tp) > 1:
+            assert tp[0][1] == 1 and tp[-1][1] == 1
 
 
 def test_migration_plan_grouping_and_order():
