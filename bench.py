@@ -832,7 +832,11 @@ def build_wave_plans(w, sources, sinks, seed=4):
         for s in sources:
             perm = (torch.randperm(half, generator=torch.Generator().manual_seed(1000 * wv + s)) + base).tolist()
             pos, given = 0, {d: 0 for d in sinks}
-            budget = {d: half / len(sinks) + carry[s][d] for d in sinks}
+            # A sink's fair share of this source's wave is proportional to what it still has to receive from the
+            # source (so that all sinks finish together), plus what it is owed from earlier waves.
+            owed = {d: sum(counts[i] for i in remaining[s][d]) for d in sinks}
+            left = sum(owed.values())
+            budget = {d: (min(half, left) * owed[d] / left if left else 0.0) + carry[s][d] for d in sinks}
 
             def give(d, i):
                 nonlocal pos
@@ -847,15 +851,21 @@ def build_wave_plans(w, sources, sinks, seed=4):
             def fits(d, i):
                 return pos + counts[i] <= half and sink_used[d] + counts[i] <= half
 
-            # first every sink's fair share (plus what it is owed), the sink that is owed most first ...
+            # first every sink's share, largest requests first, the sink that is owed most first ...
             for d in sorted(sinks, key=lambda d: -budget[d]):
                 for i in list(remaining[s][d]):
-                    if fits(d, i) and (given[d] + counts[i] <= budget[d] or given[d] == 0):
+                    if fits(d, i) and given[d] + counts[i] <= budget[d]:
                         give(d, i)
-            # ... then whatever still fits the source's half, largest first
-            for d, i in sorted(((d, i) for d in sinks for i in remaining[s][d]), key=lambda di: -counts[di[1]]):
-                if fits(d, i):
-                    give(d, i)
+            # ... then the rest of the source's half, always to the sink that is furthest below its share
+            while True:
+                pick = None
+                for d in sorted(sinks, key=lambda d: given[d] - budget[d]):
+                    pick = next(((d, i) for i in remaining[s][d] if fits(d, i)), None)
+                    if pick:
+                        break
+                if pick is None:
+                    break
+                give(*pick)
             for d in sinks:
                 carry[s][d] = max(-half, min(half, budget[d] - given[d])) if remaining[s][d] else 0.0
         assert plan.transfers, "a request does not fit an empty wave"
