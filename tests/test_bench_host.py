@@ -85,7 +85,7 @@ def test_wave_plans_use_half_pools_alternately_and_balance_the_sinks(bench, sour
     for k, plan in enumerate(plans[:-1]):
         for s in sources:
             used = sum(len(t.src_blocks) for t in plan.transfers if t.src_rank == s)
-            assert used > (0.95 if k < len(plans) - 3 else 0.75) * half
+            assert used > (0.9 if k < len(plans) - 3 else 0.75) * half
         for d in sinks:
             assert sum(len(t.src_blocks) for t in plan.transfers if t.dst_rank == d) <= half
     # the sinks' shares of a wave are proportional to what they still have to receive: before the tail no
