@@ -862,8 +862,10 @@ class V0Worker:
             totals[("o", t.src_rank)] = totals.get(("o", t.src_rank), 0) + len(t.src_blocks)
             totals[("i", t.dst_rank)] = totals.get(("i", t.dst_rank), 0) + len(t.src_blocks)
         n_ref = max(totals.values()) if totals else 0
-        chunks = plan_chunks(pool.num_layers, n_ref, page,
-                             target_bytes=getattr(self, "alltoall_chunk_bytes", ALLTOALL_MESSAGE_BYTES), taper=True)
+        # a source with many sinks splits a chunk into as many messages: keep each of them large
+        fan_out = max((len(plan.outgoing(s)) for s, _ in plan.pairs()), default=1)
+        target = getattr(self, "alltoall_chunk_bytes", ALLTOALL_MESSAGE_BYTES * max(1, min(4, fan_out // 2)))
+        chunks = plan_chunks(pool.num_layers, n_ref, page, target_bytes=target, taper=True)
         if not chunks:
             return 0
         lc_max = max_chunk_layers(chunks)
