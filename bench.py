@@ -256,7 +256,7 @@ class CpuPath:
     same seeded tables as the GPU arm; otherwise the pool is cut to `nb` blocks (stated in the result) and the
     requests keep their sizes with tables drawn inside the smaller pool."""
 
-    def __init__(self, wname, full=True):
+    def __init__(self, wname, full=True, seed=1):
         from oracle import kv_oracle
 
         self.oracle = kv_oracle
@@ -265,7 +265,7 @@ class CpuPath:
         torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
         w = self.w = WORKLOADS[wname]
         pool_gib = w["NB"] * block_bytes(w) / GIB
-        need_gib = 2 * pool_gib + 3 * max(request_blocks(w, 1)) * block_bytes(w) / GIB + 8
+        need_gib = 2 * pool_gib + 3 * max(request_blocks(w, seed)) * block_bytes(w) / GIB + 8
         self.full = bool(full and mem_available_gib() >= need_gib)
         self.nb = nb = w["NB"] if self.full else min(w["NB"], max(64, int(3 * GIB // block_bytes(w))))
         dt = DT[w["dtype"]]
@@ -281,11 +281,11 @@ class CpuPath:
             self.src.append(t)
             self.dst.append(torch.zeros(shape, dtype=dt))
         if self.full:
-            self.counts, _, self.reqs = build_requests(w, 1)
+            self.counts, _, self.reqs = build_requests(w, seed)
             self.reqs = list(self.reqs)
         else:
-            counts = [min(c, nb // 2) for c in request_blocks(w, 1)]
-            gen = torch.Generator().manual_seed(1)
+            counts = [min(c, nb // 2) for c in request_blocks(w, seed)]
+            gen = torch.Generator().manual_seed(seed)
             self.reqs = [(torch.randperm(nb, generator=gen)[:c].tolist(), torch.randperm(nb, generator=gen)[:c].tolist())
                          for c in counts]
         self.threads = torch.get_num_threads()
@@ -370,8 +370,13 @@ def reference_arm(args):
         return
     wname = {1: "llama7b_cfg1", 2: "qwen25vl7b_cfg3"}.get(args.gpus, "llava13b_cfg4")
     w = WORKLOADS[wname]
-    path = CpuPath(wname, full=True)
     n_runs = max(1, args.steps + args.warmup)
+    # Full-size host pools only where a whole step can fit the budget at all (assuming a generous 10 GB/s): the
+    # 900 GiB of config 4 cannot, and 100 GiB of host pools would be filled for a sample that never needs them.
+    seed = 1 if args.gpus == 1 else 4  # the request sizes of the GPU arm at this N
+    workload_blocks = sum(request_blocks(w, seed))
+    whole_gib = workload_blocks * block_bytes(w) / GIB
+    path = CpuPath(wname, full=whole_gib * n_runs / 10.0 <= REFERENCE_ARM_BUDGET_S, seed=seed)
     probe = path.run(max_requests=2)  # sizes the step: seconds per block on this host
     total_blocks = sum(len(s) for s, _ in path.reqs)
     est_full = probe["seconds"] / max(1, probe["blocks"]) * total_blocks
@@ -393,7 +398,7 @@ def reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(secs * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
         "config": {"workload": wname, "geometry": {k: w[k] for k in ("L", "H", "D", "BS", "NB", "dtype")},
-                   "requests": w["requests"], "blocks_per_step": total_blocks,
+                   "requests": w["requests"], "blocks_per_step": workload_blocks,
                    "sample_requests": base["requests"], "sample_blocks": base["blocks"],
                    "nb_reduced_to": base["nb_reduced_to"], "whole_workload_per_step": whole,
                    "path": "gather -> packed buffer -> scatter",
