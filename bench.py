@@ -578,7 +578,8 @@ def bench_single(args):
                    "l2": f"inputs larger than L2 (two {w['NB'] * block_bytes(w) / GIB:.0f} GiB pools, "
                          f"{min(counts) * block_bytes(w) >> 20}..{max(counts) * block_bytes(w) >> 20} MiB per launch)",
                    "blocks_per_s": round(total_blocks * args.steps / (ms / 1e3), 1)},
-        "verified_bit_exact": verified, "verified_waves": len(waves), "verified_requests": verified_requests,
+        "verified_bit_exact": verified, "verified_waves": len(waves), "waves": len(waves),
+        "verified_requests": verified_requests,
         "verified_how": "torch.equal of dst_layer[:, dst_ids] and src_layer[:, src_ids] (int16 views) per layer, "
                         "every request of every wave, on the device before timing",
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

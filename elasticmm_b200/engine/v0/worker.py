@@ -588,7 +588,7 @@ class V0Worker:
 
     def _post_flag(self, error: Optional[str]):
         """The non-blocking half of an agreement: starts the all-reduce of this rank's error flag on the
-        current stream and returns the tensor; _read_flags turns one or more of them into a verdict. On a
+        current stream and returns the tensor; _read_flags turns one or more of them into an outcome. On a
         GPU group nothing here waits for the device, so kernels queued behind the all-reduce are ordered
         after every rank's arrival without the host stalling."""
         backend = dist.get_backend(self.process_group)
