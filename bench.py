@@ -588,7 +588,8 @@ def bench_single(args):
                      "kernel": kernel_name, "algorithmic_bytes_per_launch":
                          round(2 * payload / len(reqs)), "avg_launch_us": round(ms * 1e3 / launches, 2)},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16,
-                "api": "V0Worker.extract_kv_blocks + write_kv_blocks per request, host id lists",
+                "api": "V0Worker.extract_kv_blocks + write_kv_blocks per request, host id lists (tables of up to 128 ids "
+                       "reach the device in the kernel arguments, longer ones through a pinned staging copy)",
                 "steps": e2e_steps, "ms_per_step": round(ms_e2e / e2e_steps, 3)},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),

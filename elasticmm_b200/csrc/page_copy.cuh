@@ -48,7 +48,7 @@ struct CopySide {
   uint64_t seg_stride;         // bytes one block occupies over the moved layers and planes
 };
 
-constexpr int kInlineIds = 64;  // longest table carried in the kernel arguments
+constexpr int kInlineIds = 128;  // longest table carried in the kernel arguments (2 x 512 B of the 4 KiB argument space)
 
 struct PageCopyArgs {
   CopySide src;

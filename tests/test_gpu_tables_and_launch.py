@@ -1,6 +1,6 @@
 """The ways a block table reaches the kernels, and the launch attributes of the copy kernels.
 
-Host lists of up to 64 ids travel in the kernel arguments, longer ones through the pinned staging
+Host lists of up to 128 ids travel in the kernel arguments, longer ones through the pinned staging
 ring; tables kept on the device are uploaded once with emm_upload_ids; several peers' blocks are
 packed per peer for a layer range (the packed side of an all-to-all). Every form must give what
 the reference's extract_kv_blocks / write_kv_blocks give (elasticmm/engine/v0/worker.py:578-633)."""
@@ -32,10 +32,10 @@ def _pools(ctx, dtype=torch.bfloat16):
     return src_cpu, dst_cpu, KVPool(to_gpu(src_cpu), ctx), KVPool(to_gpu(dst_cpu), ctx)
 
 
-@pytest.mark.parametrize("n", [1, 63, 64, 65, 150])
+@pytest.mark.parametrize("n", [1, 127, 128, 129, 180])
 @pytest.mark.parametrize("opts", [BULK_DEFAULT, LDG_DEFAULT], ids=vid)
 def test_host_lists_on_both_sides_of_the_inline_limit(ctx, n, opts):
-    """64 ids ride in the kernel arguments, 65 go through the staging ring: same bytes either way."""
+    """128 ids ride in the kernel arguments, 129 go through the staging ring: same bytes either way."""
     configure(ctx, **opts)
     src_cpu, dst_cpu, src, dst = _pools(ctx)
     g = torch.Generator().manual_seed(n)
