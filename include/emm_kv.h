@@ -228,8 +228,10 @@ int emm_copy_blocks(emm_pool *src, emm_pool *dst, const int32_t *d_src_ids,
 /* Host-id forms: `h_ids` are HOST int64 arrays (the reference passes Python
  * lists and uploads them with a synchronous torch.tensor(..., device=...),
  * elasticmm/engine/v0/worker.py:597,628). The ids are range checked (and,
- * for destinations, checked for duplicates) on the host, staged through a
- * pinned ring and uploaded on `stream` without a device synchronisation. */
+ * for destinations, checked for duplicates) on the host. A list of up to 128
+ * ids travels inside the kernel arguments (no copy precedes the launch); a
+ * longer one is staged through a pinned ring and uploaded on `stream` without
+ * a device synchronisation. */
 int emm_gather_h(emm_pool *pool, const int64_t *h_ids, int32_t n, void *d_packed,
                  uint64_t packed_bytes, void *stream);
 int emm_scatter_h(emm_pool *pool, const int64_t *h_ids, int32_t n, const void *d_packed,
