@@ -887,8 +887,17 @@ class V0Worker:
             a2a["out"] = torch.empty(need_out, dtype=torch.uint8, device=self.device)
         if N_in and (a2a["in"] is None or a2a["in"].numel() < need_in):
             a2a["in"] = torch.empty(need_in, dtype=torch.uint8, device=self.device)
-        tab_out = pool.many_tables([plan.tables_np(rank, d)[0] for d in sinks]) if N_out else None
-        tab_in = pool.many_tables([plan.tables_np(s, rank)[1] for s in sources], unique=True) if N_in else None
+        # The segment tables of a plan are uploaded once and kept with it (a plan that is replayed, or the waves
+        # of a long migration run again, pay no table work); the ids were checked by _check_plan_part.
+        cache = self.__dict__.setdefault("_a2a_tables", {})
+        key = (id(plan), len(plan.transfers))
+        if key not in cache:
+            if len(cache) > 64:
+                cache.clear()
+            cache[key] = (plan,
+                          pool.many_tables([plan.tables_np(rank, d)[0] for d in sinks]) if N_out else None,
+                          pool.many_tables([plan.tables_np(s, rank)[1] for s in sources]) if N_in else None)
+        _, tab_out, tab_in = cache[key]
         for st in (a2a["pack"], a2a["wire"], a2a["unpack"]):
             st.wait_stream(main)
         ev_packed = [torch.cuda.Event(), torch.cuda.Event()]
