@@ -368,7 +368,7 @@ class V0Worker:
             return pool._logical(flat.view(pool.packed_shape(n, layer_count)))
         return buffer_for
 
-    def _staged_transfer(self, sending: bool, peer: int, block_indices: List[int]) -> Dict[str, Any]:
+    def _staged_transfer(self, sending: bool, peer: int, block_indices, checked: bool = False) -> Dict[str, Any]:
         """Common body of p2p_send_kv / p2p_recv_kv: chunk schedule, staging ring, then either the
         library's own pipeline (after init_native_nccl) or the same schedule over torch P2P."""
         what = "send" if sending else "recv"
@@ -379,7 +379,8 @@ class V0Worker:
             n = len(block_indices)
             if n == 0:
                 return {"bytes": 0, "blocks": 0}
-            ids = pool.upload_ids(pool._validated(_as_host_ids(block_indices), unique=not sending))
+            host_ids = _as_host_ids(block_indices)
+            ids = pool.upload_ids(host_ids if checked else pool._validated(host_ids, unique=not sending))
             chunks = plan_chunks(pool.num_layers, n, pool.page_bytes)
             slots = self._staging_views(pool, n, chunks)
             with _range(f"emm.p2p_{what}_kv"):
@@ -737,10 +738,10 @@ class V0Worker:
             moved = self._migrate_alltoall(plan)
         else:
             for src, dst in plan.ordered_pairs():
-                if src == rank:
-                    res = self.p2p_send_kv(dst, plan.tables(src, dst)[0])
+                if src == rank:  # the plan's ids were checked above, its tables are already arrays
+                    res = self._staged_transfer(True, dst, plan.tables_np(src, dst)[0], checked=True)
                 elif dst == rank:
-                    res = self.p2p_recv_kv(src, plan.tables(src, dst)[1])
+                    res = self._staged_transfer(False, src, plan.tables_np(src, dst)[1], checked=True)
                 else:
                     continue
                 if "error" in res:
